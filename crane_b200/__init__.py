@@ -635,12 +635,23 @@ class GavipelModel(FosovikModel):
     `FosovikModel`."""
 
 
+class NifaraxModel(FosovikModel):
+    """A layer-list decoder ("architecture": "Nifarax"): the stream starts as the group-normalised embedding; each layer runs a mixer
+    and then a feed-forward, each reading its norm's output plus a short carried causal convolution of it and each gated by a sigmoid on
+    its way back.  Mixers: latent attention (one normalised low-rank row cached per token) or gated linear attention (a decay per key
+    channel, f32 state per sequence); feed-forward: sigmoid-routed clamped gated experts that read score * h, plus a per-token scaled
+    expert for every token.  A layer may reuse another layer's tensors with a state of its own; the head is the embedding table with a
+    tanh soft cap.  Same entry points and engine options as `FosovikModel`."""
+
+
 # config.json -> model class, as `model_factory::create_backend` picks a backend by architecture (crane-serve/src/engine/model_factory.rs:471-560)
 def model_class(config: dict):
     if config.get("architecture") == "Fosovik":
         return FosovikModel
     if config.get("architecture") == "Gavipel":
         return GavipelModel
+    if config.get("architecture") == "Nifarax":
+        return NifaraxModel
     if "talker_config" in config:
         return Qwen3TTSModel
     if "vision_config" in config:

@@ -1859,7 +1859,7 @@ int crane_b200_create(const char* config_json, int device_ordinal, crane_b200_mo
         m->num_sms = prop.multiProcessorCount;
         {
             cbjson::Value root = cbjson::Parser(config_json).parse();
-            if (root.type == cbjson::Value::OBJ && (root.string("architecture", "") == "Fosovik" || root.string("architecture", "") == "Gavipel")) {
+            if (root.type == cbjson::Value::OBJ && (root.string("architecture", "") == "Fosovik" || root.string("architecture", "") == "Gavipel" || root.string("architecture", "") == "Nifarax")) {
                 m->fsv = new FosovikModel();
                 m->fsv->device = device_ordinal; m->fsv->num_sms = m->num_sms;
                 m->fsv->parse(root);

@@ -5,6 +5,7 @@
 // A row's result depends on that row's sequence only: every reduction runs in an order fixed by the row's own position and the
 // launch constants, never by what else shares the step.
 #include "ragged.cuh"
+#include "ragged_dev.cuh"
 #include "decode.cuh"
 
 #include <algorithm>
@@ -12,38 +13,6 @@
 namespace cb {
 
 namespace {
-
-__device__ __forceinline__ void store_act(const ActOut& o, int r, int c, float v) {
-    if (o.f) o.f[(size_t)r * o.ldf + c] = v;
-    if (o.hi) {
-        const bf16 h = __float2bfloat16_rn(v);
-        bf16* p = o.hi + (size_t)r * o.ldb + c;
-        *p = h;
-        if (o.lo_off) p[o.lo_off] = __float2bfloat16_rn(v - __bfloat162float(h));
-    }
-}
-
-__device__ __forceinline__ void cp_async16s(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-
-// KV page elements: f32, or bf16 with an optional low-order plane `lo` elements further on (x ~= hi + lo, ~16 mantissa bits)
-template <typename KT> __device__ __forceinline__ float kv_load(const KT* p, long long lo);
-template <> __device__ __forceinline__ float kv_load<float>(const float* p, long long) { return *p; }
-template <> __device__ __forceinline__ float kv_load<bf16>(const bf16* p, long long lo) {
-    const float h = __bfloat162float(*p);
-    return lo ? h + __bfloat162float(p[lo]) : h;
-}
-template <typename KT> __device__ __forceinline__ void kv_store(KT* p, float v, long long lo);
-template <> __device__ __forceinline__ void kv_store<float>(float* p, float v, long long) { *p = v; }
-template <> __device__ __forceinline__ void kv_store<bf16>(bf16* p, float v, long long lo) {
-    const bf16 h = __float2bfloat16_rn(v);
-    *p = h;
-    if (lo) p[lo] = __float2bfloat16_rn(v - __bfloat162float(h));
-}
 
 // ---------------------------------------------------------------------------------------------------------------- rows
 __global__ void embed_scale_rows_kernel(const int* __restrict__ ids, int T, const bf16* __restrict__ embed, int W, float scale,
@@ -61,25 +30,31 @@ __global__ void dyt_rows_kernel(const float* __restrict__ x, int ldx, const int*
 }
 
 // RMS norm of a row with up to two weight vectors on the one statistic.  The sum of squares runs in a fixed order (thread-strided
-// partial sums, then a tree over the block), so a row's result does not depend on what else is in the step.
+// partial sums, then a tree over the block), so a row's result does not depend on what else is in the step.  groups > 1: the row
+// is cut into that many equal consecutive parts and each part is divided by its own root mean square.
 __global__ void __launch_bounds__(256) rms_rows_kernel(const float* __restrict__ x, int ldx, const int* __restrict__ rows, int W, float eps,
-                                                       const float* __restrict__ w1, ActOut out1, const float* __restrict__ w2, ActOut out2) {
+                                                       const float* __restrict__ w1, ActOut out1, const float* __restrict__ w2, ActOut out2, int groups) {
     __shared__ float red[8];
     const int r = blockIdx.x, src = rows ? rows[r] : r, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* xr = x + (size_t)src * ldx;
-    float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += 256) ss = fmaf(xr[c], xr[c], ss);
-    ss = warp_sum(ss);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    float tot = 0.f;
+    const int part = W / groups;
+    for (int g = 0; g < groups; ++g) {
+        const int c0 = g * part;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < part; c += 256) ss = fmaf(xr[c0 + c], xr[c0 + c], ss);
+        ss = warp_sum(ss);
+        if (g) __syncthreads();
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) tot += red[w];
-    const float inv = 1.f / sqrtf(tot / (float)W + eps);
-    for (int c = threadIdx.x; c < W; c += 256) {
-        const float v = xr[c] * inv;
-        store_act(out1, r, c, v * w1[c]);
-        if (w2) store_act(out2, r, c, v * w2[c]);
+        for (int w = 0; w < 8; ++w) tot += red[w];
+        const float inv = 1.f / sqrtf(tot / (float)part + eps);
+        for (int c = c0 + threadIdx.x; c < c0 + part; c += 256) {
+            const float v = xr[c] * inv;
+            store_act(out1, r, c, v * w1[c]);
+            if (w2) store_act(out2, r, c, v * w2[c]);
+        }
     }
 }
 
@@ -689,10 +664,11 @@ __global__ void __launch_bounds__(256) router_logits_kernel(MoeArgs a, const bf1
     if (r >= a.T) return;
     const float* h = a.h + (size_t)r * a.ldh;
     const bool vec = router_vec_ok(a.W, ldw, a.ldh);
-    for (int e0 = 0; e0 < a.E; e0 += 4) {
+    const int rows = a.E + a.n_extra;                     // (rows behind the experts': per-row scalars the feed-forward also needs)
+    for (int e0 = 0; e0 < rows; e0 += 4) {
         float z[4];
-        router_dots<4>(h, w_router + (size_t)e0 * ldw, ldw, a.W, min(4, a.E - e0), lane, vec, z);
-        if (lane < min(4, a.E - e0)) a.router_logits[(size_t)r * a.ldr + e0 + lane] = lane == 0 ? z[0] : lane == 1 ? z[1] : lane == 2 ? z[2] : z[3];
+        router_dots<4>(h, w_router + (size_t)e0 * ldw, ldw, a.W, min(4, rows - e0), lane, vec, z);
+        if (lane < min(4, rows - e0)) a.router_logits[(size_t)r * a.ldr + e0 + lane] = lane == 0 ? z[0] : lane == 1 ? z[1] : lane == 2 ? z[2] : z[3];
     }
 }
 
@@ -764,17 +740,18 @@ __global__ void __launch_bounds__(128) route_kernel(MoeArgs a) {
     const int warp = threadIdx.x >> 5, r = blockIdx.x * 4 + warp, lane = threadIdx.x & 31;
     if (r >= a.T) return;
     choose_experts(a, a.router_logits + (size_t)r * a.ldr, r, lane, scr[warp][0], scr[warp][1], scr[warp][2]);
+    if (a.n_extra > 0 && lane == 0) a.extra_out[r] = 1.f / (1.f + expf(-a.router_logits[(size_t)r * a.ldr + a.E]));
 }
 
 // Few rows (decode): router logits and the choice in one block per row.  Warp w computes the logits of experts w, w + 8, ...
 // (f32 products of the f32 row with the bf16 router rows, lanes striding the width), warp 0 then selects as route_kernel does.
 __global__ void __launch_bounds__(256) route_rows_kernel(MoeArgs a, const bf16* __restrict__ w_router, int ldw) {
-    __shared__ float z[256];
+    __shared__ float z[256 + 4];
     __shared__ float scr[3][256];
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* h = a.h + (size_t)r * a.ldh;
     const bool vec = router_vec_ok(a.W, ldw, a.ldh);
-    for (int e = warp; e < a.E; e += 8) {
+    for (int e = warp; e < a.E + a.n_extra; e += 8) {
         float acc;
         router_dots<1>(h, w_router + (size_t)e * ldw, ldw, a.W, 1, lane, vec, &acc);
         if (lane == 0) { z[e] = acc; a.router_logits[(size_t)r * a.ldr + e] = acc; }
@@ -782,6 +759,7 @@ __global__ void __launch_bounds__(256) route_rows_kernel(MoeArgs a, const bf16* 
     __syncthreads();
     if (warp != 0) return;
     choose_experts(a, z, r, lane, scr[0], scr[1], scr[2]);
+    if (a.n_extra > 0 && lane == 0) a.extra_out[r] = 1.f / (1.f + expf(-z[a.E]));
 }
 
 // Counting sort of the (row, choice) pairs by expert + the tile map of the grouped linears (32 pairs per tile).  One block.
@@ -849,31 +827,49 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(MoeArgs a) {
     for (int i = 0; i < 2; ++i) {
         const int pr = spair[ty * 2 + i];
         if (pr < 0) continue;
+        const float ws = (UP && a.scale_input) ? a.sel_w[pr] : 1.f;      // the expert reads weight * h: its first products are linear in h
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             if (UP) {
-                if (!a.gated) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc[i][j]);
-                else if (!(j & 1)) a.act[(size_t)pr * a.lda + (n >> 1)] = silu_f(acc[i][j]) * acc[i][j + 1];      // columns (2m, 2m + 1) = (gate_m, up_m)
+                if (!a.gated) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc[i][j] * ws);
+                else if (!(j & 1)) a.act[(size_t)pr * a.lda + (n >> 1)] = glu_pair_f(acc[i][j] * ws, acc[i][j + 1] * ws, a.glu_limit);      // columns (2m, 2m + 1) = (gate_m, up_m)
             } else a.y[(size_t)pr * a.ldy + n] = acc[i][j];
         }
     }
 }
 
-// x[r] += sum over the row's choices, in choice order, of weight * expert output (y rows by pair, or by place in the sorted list)
+// x[r] += sum over the row's choices, in choice order, of weight * expert output (y rows by pair, or by place in the sorted list);
+// the weight is 1 where it already multiplied the expert's input.  Optionally, before the add: an every-token expert's output times a
+// per-row scalar joins the sum, a per-column scale applies, and a sigmoid gate per element multiplies the whole.
 __global__ void moe_combine_kernel(MoeArgs a, int y_sorted) {
     const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= a.W) return;
     float s = 0.f;
     for (int k = 0; k < a.top; ++k) {
         const int pr = r * a.top + k, row = y_sorted ? a.inv[pr] : pr;
-        s = fmaf(a.sel_w[pr], a.y[(size_t)row * a.ldy + c], s);
+        s = a.scale_input ? s + a.y[(size_t)row * a.ldy + c] : fmaf(a.sel_w[pr], a.y[(size_t)row * a.ldy + c], s);
     }
-    a.x[(size_t)r * a.ldx + c] += a.out_scale ? a.out_scale[c] * s : s;
+    if (a.shared_y) s = fmaf(a.shared_w ? a.shared_w[r] : 1.f, a.shared_y[(size_t)r * a.lds + c], s);
+    if (a.out_scale) s *= a.out_scale[c];
+    if (a.gate) s *= 1.f / (1.f + expf(-(a.gate[(size_t)r * a.ldg + c] + (a.gate_bias ? a.gate_bias[c] : 0.f))));
+    a.x[(size_t)r * a.ldx + c] += s;
 }
 __global__ void moe_gather_kernel(MoeArgs a, ActOut src, ActOut dst) {
     const int i = blockIdx.x, r = a.sorted[i] / a.top;
+    if (a.scale_input) {                                    // the expert's input is weight * h, rounded as the planes round it
+        const float ws = a.sel_w[a.sorted[i]];
+        const bf16* sh = src.hi + (size_t)r * src.ldb;
+        bf16* dh = dst.hi + (size_t)i * dst.ldb;
+        for (int c = threadIdx.x; c < src.ldb; c += blockDim.x) {
+            const float v = (__bfloat162float(sh[c]) + (src.lo_off ? __bfloat162float(sh[c + src.lo_off]) : 0.f)) * ws;
+            const bf16 h = __float2bfloat16_rn(v);
+            dh[c] = h;
+            if (dst.lo_off) dh[c + dst.lo_off] = __float2bfloat16_rn(v - __bfloat162float(h));
+        }
+        return;
+    }
     const uint4* s = reinterpret_cast<const uint4*>(src.hi + (size_t)r * src.ldb);
     uint4* d = reinterpret_cast<uint4*>(dst.hi + (size_t)i * dst.ldb);
     const int n = src.ldb / 8;                              // padded widths: multiples of 8 elements
@@ -946,6 +942,7 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(MoeArgs a) {
             acc = fmaf(bf16lo(ww.z), xx[4], acc); acc = fmaf(bf16hi(ww.z), xx[5], acc); acc = fmaf(bf16lo(ww.w), xx[6], acc); acc = fmaf(bf16hi(ww.w), xx[7], acc);
         }
         acc = warp_sum(acc);
+        if (UP && a.scale_input) acc *= a.sel_w[pr];
         pair[rr] = acc;
         if (lane == 0) {
             if (UP) { if (!a.gated) a.act[(size_t)pr * a.lda + n] = gelu_erf_f(acc); }
@@ -955,7 +952,7 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(MoeArgs a) {
     // gated experts: the warp's two rows are (gate_m, up_m), m = blockIdx.x * 8 + warp
     if (UP && a.gated && lane == 0) {
         const int m = blockIdx.x * 8 + warp;
-        if (m < N) a.act[(size_t)pr * a.lda + m] = silu_f(pair[0]) * pair[1];
+        if (m < N) a.act[(size_t)pr * a.lda + m] = glu_pair_f(pair[0], pair[1], a.glu_limit);
     }
 }
 
@@ -994,8 +991,9 @@ int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, i
     return last_err();
 }
 int rms_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, float eps, const float* w1, const ActOut& out1,
-                    const float* w2, const ActOut& out2) {
-    rms_rows_kernel<<<R, 256, 0, st>>>(x, ldx, rows, W, eps, w1, out1, w2, out2);
+                    const float* w2, const ActOut& out2, int groups) {
+    if (groups < 1 || W % groups) return -1000;
+    rms_rows_kernel<<<R, 256, 0, st>>>(x, ldx, rows, W, eps, w1, out1, w2, out2, groups);
     return last_err();
 }
 int store_rows_launch(cudaStream_t st, const float* src, int lds, int T, int W, const ActOut& dst, int col0) {

@@ -37,9 +37,10 @@ int embed_scale_rows_launch(cudaStream_t st, const int* ids, int T, const bf16* 
 int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w,
                     const float* b, const ActOut& out);
 // out_k[r, c] = x[src(r), c] / sqrt(mean_c(x^2) + eps) * w_k[c] for k = 1 and (optionally) 2: two norms of the same row share its
-// statistic.  w_k holds the final multipliers (a weight stored around zero is registered as 1 + w).
+// statistic.  w_k holds the final multipliers (a weight stored around zero is registered as 1 + w).  groups > 1: the row is cut
+// into that many equal consecutive parts, each divided by its own root mean square (W % groups == 0).  out1 may be x itself.
 int rms_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, float eps, const float* w1, const ActOut& out1,
-                    const float* w2, const ActOut& out2);
+                    const float* w2, const ActOut& out2, int groups = 1);
 // dst[r, col0 + c] = src[r, c] for c < W, in every form dst carries (f32 rows, bf16 planes)
 int store_rows_launch(cudaStream_t st, const float* src, int lds, int T, int W, const ActOut& dst, int col0);
 // C[M, N] (+)= A[M, K] f32 x W[N, K]^T bf16, every product and sum in f32 (no tensor cores): the exact mode's linear, and the router's.
@@ -128,6 +129,13 @@ struct MoeArgs {
     int score_fn = 0; const float* correction = nullptr; int n_groups = 0, keep = 0;
     int gated = 0;                    // 1: up[e] is [2F, ldwu] with (gate_j, up_j) rows interleaved, act = silu(gate) * up; 0: act = gelu_erf(up)
     const float* out_scale = nullptr; // [W] per-column factor of the combined output (nullptr: 1)
+    float glu_limit = 0.f;            // gated experts: > 0 = the clamped unit min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1)
+    int scale_input = 0;              // 1: an expert reads weight * h (its output is summed unweighted) instead of having its output weighted
+    int n_extra = 0; float* extra_out = nullptr;   // w_router carries n_extra (0 or 1) more rows behind the experts': extra_out[r] = sigmoid(row E . h)
+    // the combine may also add an every-token expert and gate the sum:
+    //   x[r, c] += sigmoid(gate[r, c] + gate_bias[c]) * out_scale[c] * (sum_k y_k[c] + shared_w[r] * shared_y[r, c])      (each part optional)
+    const float* gate = nullptr; int ldg = 0; const float* gate_bias = nullptr;
+    const float* shared_y = nullptr; int lds = 0; const float* shared_w = nullptr;
 };
 // router logits (f32 products: a.h x w_router^T -> a.router_logits), softmax + top-k, then the counting sort by expert
 int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, int ldw);
@@ -138,6 +146,64 @@ int moe_experts_launch(cudaStream_t st, const MoeArgs& a);
 int moe_gather_launch(cudaStream_t st, const MoeArgs& a, const ActOut& src, const ActOut& dst);
 int moe_combine_launch(cudaStream_t st, const MoeArgs& a, bool y_sorted);
 inline int moe_max_tiles(int T, int top, int E) { return (T * top + 31) / 32 + E; }
+
+// ---- mechanisms of layers that run their sublayers one after the other (ragged_mix.cu) ------------------------------------------------
+// Causal depthwise convolution over time with a carried window: out[r, c] = (add_input ? in[r, c] : 0) + sum_k w[c, k] * u(r, k), where
+// u(r, k) is the input taps - 1 - k tokens before row r: a row of the same entry, or the sequence's window (its last taps - 1 inputs,
+// zeros for a new sequence).  The window is moved on afterwards.  single_rows: every entry brings one row (both in one launch).
+struct CausalConvArgs {
+    const float* in; int ld;          // [T, ld]
+    int C, taps;
+    const float* w;                   // [C, taps]
+    float* state;                     // [slots, taps - 1, C]
+    int add_input;
+    ActOut out;
+    int single_rows = 0;
+};
+int causal_conv_launch(cudaStream_t st, const RaggedBatch& rb, const CausalConvArgs& a);
+int causal_conv_launch_count(const CausalConvArgs& a);
+
+// x[r, c] += sigmoid(gate[r, c] + bias[c]) * y[r, c]
+int gated_add_launch(cudaStream_t st, float* x, int ldx, const float* y, int ldy, const float* gate, int ldg, const float* bias, int T, int W);
+
+// Latent attention, first half: proj [T, ld] holds the query latent (q_rank columns) and the key / value latent (kv_rank columns).
+// Each is RMS-normed with its weight; the query latent goes to cq, the key / value latent to the sequence's page at the row's position
+// (one "head" of width kv_rank: the pool serves as keys and as values).
+struct LatentPrepArgs {
+    const float* proj; int ld;
+    int q_rank, kv_rank;
+    const float* q_w; const float* kv_w;
+    float eps;
+    ActOut cq;
+    void* pool; int kv_f32; long long kv_lo_off;
+    const int* block_table; int max_pages;
+};
+int latent_prep_launch(cudaStream_t st, const RaggedBatch& rb, const LatentPrepArgs& a);
+
+// Block-diagonal linear: out[r, h * n_out + i] = sum_j in[r, h * n_in + j] * w[(h * n_in + j) * n_out + i], every product and sum in
+// f32 in the order j = 0, 1, ...  (w is stored input-major per head: [H, n_in, n_out] bf16).
+int headwise_linear_launch(cudaStream_t st, const ActOut& in, const bf16* w, int T, int H, int n_in, int n_out, const ActOut& out);
+
+// Gated linear attention.  proj [T, ld] holds q | k | v | g | a (H*d, H*d, H*dv, H*dv, rank columns).  Per head and key channel the
+// decay is sigmoid(z)^(1 / tau), z = a2 a + b (all f32); S_t = diag(decay_t) S_(t-1) + k_t v_t^T; o_t = S_t^T (q_t * q_scale); then
+// out = rms_norm_over_dv(o) * norm_w * silu(g).  The state [slots, H, d, dv] is f32 and carried in place.
+struct GlaArgs {
+    const float* proj; int ld;
+    int H, d, dv, rank;
+    const float* a2;                  // [H * d, rank] f32
+    const float* a2_b;                // [H * d]
+    float inv_tau, q_scale, eps;
+    const float* norm_w;              // [dv]
+    float* state;
+    float* decay;                     // [T, H * d] scratch
+    float* y;                         // [T, H * dv] scratch
+    ActOut out;                       // [T, H * dv]
+};
+int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a);
+constexpr int GLA_LAUNCHES = 3;
+
+// dst[r, c] = cap * tanh(src[r, c] / cap) for c < V (cap <= 0: a plain copy)
+int softcap_rows_launch(cudaStream_t st, const float* src, int lds, int R, int V, float cap, float* dst, int ldd);
 
 // Greedy feedback for on-device decode loops: token = argmax of logits row e (lowest index among maxima; 64 partial results per
 // row in part_val / part_idx, then one block) -> ids[e], recorded at out[e * out_stride + *step]; row_pos[e] and ent_pos0[e] move on

@@ -1,0 +1,332 @@
+// Ragged-batch kernels of layers that run their sublayers one after the other (see ragged.cuh): a carried causal convolution in
+// front of a sublayer, a sigmoid gate on its way back into the residual, latent attention (only a normalised low-rank row is kept
+// per token; the per-head key and value maps are applied to the query and to the attention's output instead), gated linear
+// attention with a decay per key channel, and a soft cap on the logits.  All of it is f32 arithmetic on CUDA cores; a row's result
+// depends on its own sequence only (every sum runs in an order fixed by the row's position and the launch constants).
+#include "ragged.cuh"
+#include "ragged_dev.cuh"
+#include "decode.cuh"
+
+#include <algorithm>
+
+namespace cb {
+
+namespace {
+
+inline int last_err() { return (int)cudaGetLastError(); }
+
+// ---------------------------------------------------------------------------------------------------------------- convolution
+__global__ void causal_conv_rows_kernel(RaggedBatch rb, CausalConvArgs a) {
+    const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int e = rb.row_entry[r], i = r - rb.ent_row0[e], slot = rb.ent_slot[e], taps = a.taps;
+    const float* win = a.state + (size_t)slot * (taps - 1) * a.C;
+    const float own = a.in[(size_t)r * a.ld + c];
+    float acc = 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int back = taps - 1 - k;                   // this tap reads the input `back` tokens ago
+        const float u = back == 0 ? own : (i - back >= 0) ? a.in[(size_t)(r - back) * a.ld + c] : win[(size_t)(taps - 1 + i - back) * a.C + c];
+        acc = fmaf(a.w[(size_t)c * taps + k], u, acc);
+    }
+    store_act(a.out, r, c, a.add_input ? own + acc : acc);
+}
+// New window = the last taps - 1 inputs of the sequence (older ones shift down when the entry is shorter than the window).
+__global__ void causal_conv_window_kernel(RaggedBatch rb, CausalConvArgs a) {
+    const int e = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e], nwin = a.taps - 1;
+    float* win = a.state + (size_t)slot * nwin * a.C;
+    for (int i = 0; i < nwin; ++i) {
+        const int src = len - nwin + i;                  // index among this entry's rows
+        win[(size_t)i * a.C + c] = (src >= 0) ? a.in[(size_t)(r0 + src) * a.ld + c] : win[(size_t)(i + len) * a.C + c];
+    }
+}
+// Every entry one token: the convolution and the window shift in one pass; thread = (entry, channel) owns its window column.
+__global__ void causal_conv_step_kernel(RaggedBatch rb, CausalConvArgs a) {
+    const int e = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int r = rb.ent_row0[e], slot = rb.ent_slot[e], taps = a.taps;
+    float* win = a.state + (size_t)slot * (taps - 1) * a.C;
+    const float u = a.in[(size_t)r * a.ld + c];
+    float acc = 0.f;
+    for (int k = 0; k < taps - 1; ++k) {
+        const float w = win[(size_t)k * a.C + c];
+        acc = fmaf(a.w[(size_t)c * taps + k], w, acc);
+        if (k > 0) win[(size_t)(k - 1) * a.C + c] = w;
+    }
+    acc = fmaf(a.w[(size_t)c * taps + taps - 1], u, acc);
+    if (taps > 1) win[(size_t)(taps - 2) * a.C + c] = u;
+    store_act(a.out, r, c, a.add_input ? u + acc : acc);
+}
+
+__global__ void gated_add_kernel(float* __restrict__ x, int ldx, const float* __restrict__ y, int ldy, const float* __restrict__ gate, int ldg,
+                                 const float* __restrict__ bias, int W) {
+    const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const float g = gate[(size_t)r * ldg + c] + (bias ? bias[c] : 0.f);
+    x[(size_t)r * ldx + c] += y[(size_t)r * ldy + c] / (1.f + expf(-g));
+}
+
+__global__ void softcap_rows_kernel(const float* __restrict__ src, int lds, int V, float cap, float* __restrict__ dst, int ldd) {
+    const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= V) return;
+    const float z = src[(size_t)r * lds + c];
+    dst[(size_t)r * ldd + c] = cap > 0.f ? cap * tanhf(z / cap) : z;
+}
+
+// ---------------------------------------------------------------------------------------------------------------- latent attention
+// Block per row: the two latents one after the other, each with its own sum of squares (thread-strided partial sums, then a fixed
+// tree), the second stored into the sequence's page.
+template <typename KT>
+__global__ void __launch_bounds__(256) latent_prep_kernel(RaggedBatch rb, LatentPrepArgs a) {
+    __shared__ float red[8];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = rb.row_entry[r], pos = rb.row_pos[r], slot = rb.ent_slot[e];
+    const int page = a.block_table[(size_t)slot * a.max_pages + pos / KV_PAGE];
+    KT* dst = (KT*)a.pool + ((size_t)page * KV_PAGE + (pos % KV_PAGE)) * a.kv_rank;
+    for (int seg = 0; seg < 2; ++seg) {
+        const int n = seg ? a.kv_rank : a.q_rank;
+        const float* src = a.proj + (size_t)r * a.ld + (seg ? a.q_rank : 0);
+        const float* w = seg ? a.kv_w : a.q_w;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < n; c += 256) ss = fmaf(src[c], src[c], ss);
+        ss = warp_sum(ss);
+        if (seg) __syncthreads();
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tot += red[k];
+        const float inv = 1.f / sqrtf(tot / (float)n + a.eps);
+        for (int c = threadIdx.x; c < n; c += 256) {
+            const float v = src[c] * inv * w[c];
+            if (seg) kv_store<KT>(dst + c, v, a.kv_lo_off);
+            else store_act(a.cq, r, c, v);
+        }
+    }
+}
+
+// Block = (HW_ROWS rows, head): the rows' input slices sit in shared memory, a thread owns output columns i, i + 128, ... and walks the
+// head's [n_in, n_out] matrix down its column (neighbouring threads read neighbouring weights).
+constexpr int HW_ROWS = 8;
+__device__ __forceinline__ float act_load(const ActOut& o, int r, int c) {
+    if (o.f) return o.f[(size_t)r * o.ldf + c];
+    const bf16* p = o.hi + (size_t)r * o.ldb + c;
+    return __bfloat162float(*p) + (o.lo_off ? __bfloat162float(p[o.lo_off]) : 0.f);
+}
+__global__ void __launch_bounds__(128) headwise_linear_kernel(ActOut in, const bf16* __restrict__ w, int T, int n_in, int n_out, ActOut out) {
+    extern __shared__ float hw_in[];                      // [HW_ROWS][n_in]
+    const int r0 = blockIdx.x * HW_ROWS, h = blockIdx.y, nr = min(HW_ROWS, T - r0);
+    for (int i = threadIdx.x; i < HW_ROWS * n_in; i += blockDim.x) {
+        const int rr = i / n_in, j = i - rr * n_in;
+        hw_in[i] = rr < nr ? act_load(in, r0 + rr, h * n_in + j) : 0.f;
+    }
+    __syncthreads();
+    const bf16* wh = w + (size_t)h * n_in * n_out;
+    for (int i = threadIdx.x; i < n_out; i += blockDim.x) {
+        float acc[HW_ROWS];
+#pragma unroll
+        for (int rr = 0; rr < HW_ROWS; ++rr) acc[rr] = 0.f;
+        for (int j = 0; j < n_in; ++j) {
+            const float wv = __bfloat162float(wh[(size_t)j * n_out + i]);
+#pragma unroll
+            for (int rr = 0; rr < HW_ROWS; ++rr) acc[rr] = fmaf(hw_in[rr * n_in + j], wv, acc[rr]);
+        }
+#pragma unroll
+        for (int rr = 0; rr < HW_ROWS; ++rr) if (rr < nr) store_act(out, r0 + rr, h * n_out + i, acc[rr]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------- gated linear attention
+// decay[r, c] = sigmoid(z)^(1 / tau) = exp(log_sigmoid(z) / tau), z = a2[c, :] . a[r, :] + b[c]; log_sigmoid(z) = min(z, 0) - log1p(e^-|z|)
+__global__ void __launch_bounds__(256) gla_decay_kernel(GlaArgs a) {
+    extern __shared__ float lowrank[];                    // [rank]
+    const int r = blockIdx.x, C = a.H * a.d;
+    const float* src = a.proj + (size_t)r * a.ld + 2 * C + 2 * a.H * a.dv;
+    for (int j = threadIdx.x; j < a.rank; j += blockDim.x) lowrank[j] = src[j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float z = a.a2_b[c];
+        const float* row = a.a2 + (size_t)c * a.rank;
+        for (int j = 0; j < a.rank; ++j) z = fmaf(row[j], lowrank[j], z);
+        const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+        a.decay[(size_t)r * C + c] = expf(ls * a.inv_tau);
+    }
+}
+
+// The recurrence.  Block = (entry, head, slice of GLA_COLS value columns); thread (p, ns) keeps state rows ns * R .. ns * R + R - 1 of
+// column p in registers for the whole portion.  One token costs one multiply-add per state element and another for the output, so
+// what would serialise the loop is fetching its operands: the step inputs (v slice, k, q, decay) of GLA_CH tokens at a time are
+// staged in shared memory with cp.async, double-buffered.  Every R-run of a staged vector is followed by 4 pad floats, which
+// spreads the eight runs a warp reads at once over all banks; rows past d stay zero from the start and leave the state at zero.
+constexpr int GLA_NS = 8, GLA_COLS = 16, GLA_CH = 16;
+__host__ __device__ inline int gla_idx(int n, int R) { return n + 4 * (n / R); }
+__host__ __device__ inline int gla_npad(int R) { return 8 * (R + 4); }
+template <int R>
+__global__ void __launch_bounds__(GLA_COLS * GLA_NS) gla_scan_kernel(RaggedBatch rb, GlaArgs a) {
+    extern __shared__ __align__(16) float gla_s[];
+    const int e = blockIdx.x, h = blockIdx.y, ns = threadIdx.x & (GLA_NS - 1), pl = threadIdx.x / GLA_NS;
+    const int p0 = blockIdx.z * GLA_COLS, p = p0 + pl;
+    const int d = a.d, dv = a.dv, C = a.H * d;
+    const bool live = p < dv;
+    const int len = rb.ent_len[e], slot = rb.ent_slot[e], r0 = rb.ent_row0[e];
+    const int ncol = min(GLA_COLS, dv - p0);
+    const int NP = gla_npad(R), per_tok = GLA_COLS + 3 * NP;
+    float* stage[2] = {gla_s, gla_s + GLA_CH * per_tok};
+    float* S = a.state + (((size_t)slot * a.H + h) * d) * dv;
+    const int n0 = ns * R;
+    for (int i = threadIdx.x; i < 2 * GLA_CH * per_tok; i += blockDim.x) gla_s[i] = 0.f;
+    __syncthreads();
+    float s[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) s[i] = (n0 + i < d && live) ? S[(size_t)(n0 + i) * dv + p] : 0.f;
+    const int qoff = h * d, koff = C + h * d, voff = 2 * C + h * dv + p0;
+    // 16-byte copies when every piece starts on a 16-byte boundary (the usual geometry), 4-byte copies otherwise
+    const bool wide = ((d | dv | a.ld | C) & 3) == 0 && (R & 3) == 0;
+    auto fetch = [&](int c, float* dst) {                     // tokens [c * GLA_CH, ...) of the portion
+        const int t0 = c * GLA_CH, nt = min(GLA_CH, len - t0);
+        if (wide) {                                           // 8 threads per token: v (4 pieces), then k, q, decay (d / 4 pieces each)
+            const int t = threadIdx.x >> 3, q = threadIdx.x & 7, nq = d >> 2;
+            if (t < nt) {
+                const float* row = a.proj + (size_t)(r0 + t0 + t) * a.ld;
+                const float* dec = a.decay + (size_t)(r0 + t0 + t) * C + h * d;
+                float* d0 = dst + t * per_tok;
+                for (int k = q; k < GLA_COLS / 4 + 3 * nq; k += 8) {
+                    if (k < GLA_COLS / 4) { if (4 * k < ncol) cp_async16s(d0 + 4 * k, row + voff + 4 * k); }
+                    else {
+                        const int which = (k - GLA_COLS / 4) / nq, n = 4 * ((k - GLA_COLS / 4) % nq);
+                        const float* src = which == 0 ? row + koff + n : which == 1 ? row + qoff + n : dec + n;
+                        cp_async16s(d0 + GLA_COLS + which * NP + gla_idx(n, R), src);
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
+        const int src_tok = GLA_COLS + 3 * d;
+        for (int i = threadIdx.x; i < nt * src_tok; i += blockDim.x) {
+            const int t = i / src_tok, j = i - t * src_tok, r = r0 + t0 + t;
+            const float* row = a.proj + (size_t)r * a.ld;
+            const float* src;
+            int o;
+            if (j < GLA_COLS) { if (j >= ncol) continue; src = row + voff + j; o = j; }
+            else {
+                const int which = (j - GLA_COLS) / d, n = (j - GLA_COLS) % d;
+                src = which == 0 ? row + koff + n : which == 1 ? row + qoff + n : a.decay + (size_t)r * C + h * d + n;
+                o = GLA_COLS + which * NP + gla_idx(n, R);
+            }
+            cp_async4(dst + t * per_tok + o, src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nch = (len + GLA_CH - 1) / GLA_CH;
+    fetch(0, stage[0]);
+    for (int c = 0; c < nch; ++c) {
+        if (c + 1 < nch) { fetch(c + 1, stage[(c + 1) & 1]); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float* st = stage[c & 1];
+        const int nt = min(GLA_CH, len - c * GLA_CH);
+        for (int t = 0; t < nt; ++t) {
+            const float* tk = st + t * per_tok;
+            const float xv = live ? tk[pl] : 0.f;
+            const float* kp = tk + GLA_COLS + gla_idx(n0, R);
+            float y0 = 0.f, y1 = 0.f;
+            if ((R & 3) == 0) {
+                const float4* K4 = reinterpret_cast<const float4*>(kp);
+                const float4* Q4 = reinterpret_cast<const float4*>(kp + NP);
+                const float4* A4 = reinterpret_cast<const float4*>(kp + 2 * NP);
+#pragma unroll
+                for (int i = 0; i < R / 4; ++i) {
+                    const float4 k = K4[i], q = Q4[i], al = A4[i];
+                    s[4 * i]     = fmaf(al.x, s[4 * i],     k.x * xv); y0 = fmaf(s[4 * i],     q.x, y0);
+                    s[4 * i + 1] = fmaf(al.y, s[4 * i + 1], k.y * xv); y1 = fmaf(s[4 * i + 1], q.y, y1);
+                    s[4 * i + 2] = fmaf(al.z, s[4 * i + 2], k.z * xv); y0 = fmaf(s[4 * i + 2], q.z, y0);
+                    s[4 * i + 3] = fmaf(al.w, s[4 * i + 3], k.w * xv); y1 = fmaf(s[4 * i + 3], q.w, y1);
+                }
+            }
+            float y = y0 + y1;
+#pragma unroll
+            for (int o = GLA_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (ns == 0 && live) a.y[(size_t)(r0 + c * GLA_CH + t) * a.H * dv + h * dv + p] = y * a.q_scale;
+        }
+        __syncthreads();                                      // the stage is free for chunk c + 2
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) if (n0 + i < d && live) S[(size_t)(n0 + i) * dv + p] = s[i];
+}
+
+// out[r, h * dv + c] = y / sqrt(mean_c(y^2) + eps) * w[c] * silu(g[r, h * dv + c]): one warp per (row, head)
+__global__ void __launch_bounds__(128) gla_out_kernel(GlaArgs a, int T) {
+    const int r = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (h >= a.H) return;
+    const int dv = a.dv;
+    const float* y = a.y + (size_t)r * a.H * dv + h * dv;
+    const float* g = a.proj + (size_t)r * a.ld + 2 * a.H * a.d + a.H * dv + h * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(y[c], y[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)dv + a.eps);
+    for (int c = lane; c < dv; c += 32) store_act(a.out, r, h * dv + c, y[c] * inv * a.norm_w[c] * silu_f(g[c]));
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------- launchers
+int causal_conv_launch_count(const CausalConvArgs& a) { return (a.single_rows || a.taps <= 1) ? 1 : 2; }
+int causal_conv_launch(cudaStream_t st, const RaggedBatch& rb, const CausalConvArgs& a) {
+    if (a.taps < 1 || a.C < 1 || !a.in) return -1000;
+    const dim3 grid((a.C + 127) / 128, a.single_rows ? rb.E : rb.T);
+    if (a.single_rows) {
+        causal_conv_step_kernel<<<grid, 128, 0, st>>>(rb, a);
+        return last_err();
+    }
+    causal_conv_rows_kernel<<<grid, 128, 0, st>>>(rb, a);
+    if (const int e = last_err()) return e;
+    if (a.taps > 1) causal_conv_window_kernel<<<dim3((a.C + 127) / 128, rb.E), 128, 0, st>>>(rb, a);
+    return last_err();
+}
+int gated_add_launch(cudaStream_t st, float* x, int ldx, const float* y, int ldy, const float* gate, int ldg, const float* bias, int T, int W) {
+    gated_add_kernel<<<dim3((W + 127) / 128, T), 128, 0, st>>>(x, ldx, y, ldy, gate, ldg, bias, W);
+    return last_err();
+}
+int softcap_rows_launch(cudaStream_t st, const float* src, int lds, int R, int V, float cap, float* dst, int ldd) {
+    softcap_rows_kernel<<<dim3((V + 255) / 256, R), 256, 0, st>>>(src, lds, V, cap, dst, ldd);
+    return last_err();
+}
+int latent_prep_launch(cudaStream_t st, const RaggedBatch& rb, const LatentPrepArgs& a) {
+    if (a.q_rank < 1 || a.kv_rank < 1) return -1000;
+    if (a.kv_f32) latent_prep_kernel<float><<<rb.T, 256, 0, st>>>(rb, a);
+    else latent_prep_kernel<bf16><<<rb.T, 256, 0, st>>>(rb, a);
+    return last_err();
+}
+int headwise_linear_launch(cudaStream_t st, const ActOut& in, const bf16* w, int T, int H, int n_in, int n_out, const ActOut& out) {
+    const size_t smem = (size_t)HW_ROWS * n_in * sizeof(float);
+    if ((!in.f && !in.hi) || smem > 200 * 1024) return -1000;
+    static SmemOptIn seen;
+    if (const int e = ensure_dyn_smem(headwise_linear_kernel, smem, seen)) return e;
+    headwise_linear_kernel<<<dim3((T + HW_ROWS - 1) / HW_ROWS, H), 128, smem, st>>>(in, w, T, n_in, n_out, out);
+    return last_err();
+}
+int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a) {
+    if (a.d < 1 || a.d > 256 || a.dv < 1 || a.rank < 1 || a.rank > 8192) return -1000;
+    gla_decay_kernel<<<rb.T, 256, (size_t)a.rank * sizeof(float), st>>>(a);
+    int e = last_err();
+    if (e) return e;
+    const int nr = (a.d + GLA_NS - 1) / GLA_NS, R = nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
+    const size_t smem = (size_t)2 * GLA_CH * (GLA_COLS + 3 * gla_npad(R)) * sizeof(float);      // <= 113 KB at d = 256
+    const dim3 grid(rb.E, a.H, (a.dv + GLA_COLS - 1) / GLA_COLS);
+    auto run = [&](auto kern, SmemOptIn& seen) -> int {
+        if (const int er = ensure_dyn_smem(kern, smem, seen)) return er;
+        kern<<<grid, GLA_COLS * GLA_NS, smem, st>>>(rb, a);
+        return last_err();
+    };
+    static SmemOptIn seen[4];
+    e = R == 4 ? run(gla_scan_kernel<4>, seen[0]) : R == 8 ? run(gla_scan_kernel<8>, seen[1]) : R == 16 ? run(gla_scan_kernel<16>, seen[2])
+                                                                                                        : run(gla_scan_kernel<32>, seen[3]);
+    if (e) return e;
+    gla_out_kernel<<<dim3(rb.T, (a.H + 3) / 4), 128, 0, st>>>(a, rb.T);
+    return last_err();
+}
+
+}  // namespace cb

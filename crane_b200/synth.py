@@ -440,7 +440,89 @@ def gavipel_tensor_specs(cfg: dict):
     yield "final.norm", (W,), "norm0"
 
 
+def nifarax_config(width=1024, vocab=65536, layers=12, gla_every=3, heads=8, dim=128, vdim=128, q_rank=512, kv_rank=256, gla_heads=8,
+                   gla_dim=64, gla_vdim=128, tau=16.0, decay_rank=32, experts=8, top=4, expert_ff=896, shared_ff=896, limit=7.0, taps=4,
+                   norm_groups=2, share_last_gla=True):
+    """`layers` layers, every `gla_every`-th one gated linear attention and the others latent attention, each with a mixture of clamped
+    gated experts and a shared expert; the last gla layer reuses the first one's tensors.  `decay_rank` is not read by the engine (the
+    rank comes with the tensors); it tells `nifarax_tensor_specs` which shape to make."""
+    att = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": dim ** -0.5}
+    gla = {"heads": gla_heads, "dim": gla_dim, "vdim": gla_vdim, "tau": tau, "decay_rank": decay_rank}
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+    if shared_ff:
+        mlp["shared"] = {"ff": shared_ff, "limit": limit}
+    ls, first_gla = [], None
+    for i in range(layers):
+        if gla_every and i % gla_every == gla_every - 1:
+            ls.append({"type": "gla", "mixer": dict(gla), "mlp": dict(mlp)})
+            first_gla = i if first_gla is None else first_gla
+        else:
+            ls.append({"type": "latent_attention", "mixer": dict(att), "mlp": dict(mlp)})
+    glas = [i for i, L in enumerate(ls) if L["type"] == "gla"]
+    if share_last_gla and len(glas) > 1:
+        ls[glas[-1]]["weights_of"] = glas[0]
+    return {"architecture": "Nifarax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": norm_groups}, "canon": {"taps": taps},
+            "logit_softcap": 30.0, "layers": ls}
+
+
+def nifarax_tensor_specs(cfg: dict):
+    """(name, shape, kind): 'embed', 'embed.norm', 'final.norm', 'l<i>.norm1|norm2|canon1|canon2|rg1|rg1.b|rg2|rg2.b',
+    'l<i>.mix.dq|dq.norm|uq|dkv|dkv.norm|uk|uv|o' or 'l<i>.mix.q|k|v|g|o|norm|a1|a2|a2.b', 'l<i>.mlp.e<j>.gate|up|down',
+    'l<i>.mlp.router', 'l<i>.mlp.shared.gate|up|down|sg'.  A layer with 'weights_of' has none."""
+    W, V, taps = cfg["width"], cfg["vocab"], cfg["canon"]["taps"]
+    yield "embed", (V, W), "embed"
+    yield "embed.norm", (W,), "norm"
+    for i, L in enumerate(cfg["layers"]):
+        if L.get("weights_of") is not None:
+            continue
+        p, m = f"l{i}.", L["mixer"]
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        yield p + "norm1", (W,), "norm"
+        yield p + "canon1", (W, taps), "linear"
+        yield p + "rg1", (W, W), "linear"
+        yield p + "rg1.b", (W,), "bias"
+        if L["type"] == "gla":
+            r = m.get("decay_rank", 16)
+            yield p + "mix.q", (H * d, W), "linear"
+            yield p + "mix.k", (H * d, W), "linear"
+            yield p + "mix.v", (H * dv, W), "linear"
+            yield p + "mix.g", (H * dv, W), "linear"
+            yield p + "mix.a1", (r, W), "linear"
+            yield p + "mix.a2", (H * d, r), "linear"
+            yield p + "mix.a2.b", (H * d,), "dt_bias"
+            yield p + "mix.norm", (dv,), "norm"
+        else:
+            yield p + "mix.dq", (m["q_rank"], W), "linear"
+            yield p + "mix.dq.norm", (m["q_rank"],), "norm"
+            yield p + "mix.uq", (H * d, m["q_rank"]), "linear"
+            yield p + "mix.dkv", (m["kv_rank"], W), "linear"
+            yield p + "mix.dkv.norm", (m["kv_rank"],), "norm"
+            yield p + "mix.uk", (H * d, m["kv_rank"]), "linear"
+            yield p + "mix.uv", (H * dv, m["kv_rank"]), "linear"
+        yield p + "mix.o", (W, H * dv), "linear"
+        f = L.get("mlp")
+        if f:
+            yield p + "norm2", (W,), "norm"
+            yield p + "canon2", (W, taps), "linear"
+            yield p + "rg2", (W, W), "linear"
+            yield p + "rg2.b", (W,), "bias"
+            for e in range(f["router"]["experts"]):
+                yield f"{p}mlp.e{e}.gate", (f["expert"]["ff"], W), "linear"
+                yield f"{p}mlp.e{e}.up", (f["expert"]["ff"], W), "linear"
+                yield f"{p}mlp.e{e}.down", (W, f["expert"]["ff"]), "linear"
+            yield p + "mlp.router", (f["router"]["experts"], W), "linear"
+            if f.get("shared"):
+                yield p + "mlp.shared.gate", (f["shared"]["ff"], W), "linear"
+                yield p + "mlp.shared.up", (f["shared"]["ff"], W), "linear"
+                yield p + "mlp.shared.down", (W, f["shared"]["ff"]), "linear"
+                yield p + "mlp.shared.sg", (1, W), "linear"
+    yield "final.norm", (W,), "norm"
+
+
 def tensor_specs(cfg: dict):
+    if cfg.get("architecture") == "Nifarax":
+        yield from nifarax_tensor_specs(cfg)
+        return
     if cfg.get("architecture") == "Fosovik":
         yield from fosovik_tensor_specs(cfg)
         return
