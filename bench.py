@@ -570,6 +570,135 @@ def bench_gavipel(args, rank, world, local_rank):
     print(json.dumps(out))
 
 
+def bench_nifarax(args, rank, world, local_rank):
+    """The Nifarax layer-list decoder (latent attention and gated linear attention behind carried convolutions, gated residuals, clamped
+    experts that read score * h, a shared expert) beside the closest existing model, a Fosovik stack with the same order of attention
+    and recurrent (Mamba-2) layers and erf-GELU experts, at equal width, depth, heads and experts, at two sizes.  One request =
+    4096-token prefill + 256 greedy tokens through `crane_b200_generate_greedy`; random bf16 blocks as weights (timing only; the
+    routers are drawn properly so that the experts share the rows); one GPU."""
+    import crane_b200
+    sys.path.insert(0, os.path.join(ROOT, "tools"))
+    import bench_configs as bc
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no model of this design"}))
+        return
+    if rank != 0:
+        return
+    S, n_dec = 4096, 256
+    peaks = load_peaks()
+    sampler = ClockSampler(0)
+
+    def closest(width, layers, every, heads, dim, r_heads, r_vdim, state, moe):
+        c = synth.fosovik_config(width=width, vocab=65536, blocks=1, attn_every=2, heads=heads, kv_heads=max(heads // 4, 1), dim=dim, ssm_heads=r_heads,
+                                 ssm_vdim=r_vdim, state=state, groups=1, moe=moe)
+        rec, att = c["layers"]
+        c["layers"] = [dict(rec) if i % every == every - 1 else dict(att) for i in range(layers)]
+        return c
+    sizes = {
+        "w1024_12layers_8x896_top4": dict(
+            nif=synth.nifarax_config(width=1024, layers=12, gla_every=3, heads=8, dim=128, vdim=128, q_rank=512, kv_rank=256, gla_heads=8, gla_dim=64,
+                                     gla_vdim=128, decay_rank=32, experts=8, top=4, expert_ff=896, shared_ff=896),
+            fsv=closest(1024, 12, 3, 8, 128, 8, 128, 64, (8, 4, 896))),
+        "w2048_9layers_16x1024_top4": dict(
+            nif=synth.nifarax_config(width=2048, layers=9, gla_every=3, heads=16, dim=128, vdim=128, q_rank=768, kv_rank=256, gla_heads=16, gla_dim=64,
+                                     gla_vdim=128, decay_rank=64, experts=16, top=4, expert_ff=1024, shared_ff=2048),
+            fsv=closest(2048, 9, 3, 16, 128, 16, 128, 64, (16, 4, 1024))),
+    }
+
+    def load(cls, cfg):
+        m = cls(cfg, device=0, max_tokens=S + n_dec + 128, max_batch=4)
+        for name, shape, kind in synth.tensor_specs(cfg):
+            proper = name.endswith(("mlp.router", "mlp.shared.sg", "mix.a1", "mix.a2", "mix.a2.b"))
+            m.load_tensor(name, synth.make_tensor(name, shape, kind) if proper else bc.cheap(shape, kind))
+        m.finalize()
+        return m
+
+    def work(cfg):
+        """(weights a token touches, attention flops of the prompt, bytes of cache and state a decode step touches)"""
+        W, V = cfg["width"], cfg["vocab"]
+        shapes = {n: sh for n, sh, k in synth.tensor_specs(cfg)}
+        per_tok, attn_fl, cache_b = V * W, 0.0, 0.0
+        ctx = S + n_dec / 2
+        for i, L in enumerate(cfg["layers"]):
+            src = L.get("weights_of", i) if L.get("weights_of") is not None else i
+            mats = {n: sh for n, sh in shapes.items() if n.startswith(f"l{src}.") and len(sh) == 2 and "canon" not in n and ".mix.conv" not in n}
+            f = L.get("mlp")
+            for n, sh in mats.items():
+                share = f["router"]["top"] / f["router"]["experts"] if ".mlp.e" in n else 1.0
+                per_tok += share * sh[0] * sh[1]
+            a = L["mixer"]
+            if L["type"] == "latent_attention":        # scores and sums at the heads' own widths; one latent row (hi + lo planes) per cached token
+                attn_fl += 2.0 * S * (S / 2) * a["heads"] * (a["dim"] + a["vdim"])
+                cache_b += ctx * a["kv_rank"] * 4
+            elif L["type"] == "attention":
+                attn_fl += 4.0 * S * (S / 2) * a["heads"] * a["dim"]
+                cache_b += ctx * 2 * a["kv_heads"] * a["dim"] * 4
+            elif L["type"] == "gla":
+                attn_fl += 4.0 * S * a["heads"] * a["dim"] * a["vdim"]
+                cache_b += 2 * 4 * a["heads"] * a["dim"] * a["vdim"]
+            else:
+                attn_fl += 4.0 * S * a["heads"] * a["state"] * a["vdim"]
+                cache_b += 2 * 4 * a["heads"] * a["state"] * a["vdim"]
+        return per_tok, attn_fl, cache_b
+
+    def measure(m, cfg, tag):
+        ids = synth.synth_token_ids(S, cfg["vocab"], tag)
+
+        def request():
+            m.clear_kv_cache()
+            t0 = time.perf_counter()
+            out = m.generate_greedy(ids, n_dec + 1)
+            wall = time.perf_counter() - t0
+            t = m.last_timing()
+            return wall, t["prefill_ms"], t["decode_ms"], len(out) - 1
+        for _ in range(max(args.warmup, 3)):
+            request()
+        l0 = m.kernel_launches()
+        rs = [request() for _ in range(args.steps)]
+        launches = m.kernel_launches() - l0
+        per_tok, attn_fl, cache_b = work(cfg)
+        W, V = cfg["width"], cfg["vocab"]
+        fl = 2.0 * (per_tok - V * W) * S + attn_fl + 2.0 * V * W
+        by = 2.0 * per_tok + cache_b
+        dec_s, ntok, pre_s = sum(r[2] for r in rs) / 1e3, sum(r[3] for r in rs), sum(r[1] for r in rs) / 1e3
+        return {"decode_tok_s": ntok / dec_s, "decode_us_per_step": 1e6 * dec_s / ntok, "prefill_ms": 1e3 * pre_s / len(rs),
+                "prefill_tok_s": S * len(rs) / pre_s, "prefill_tflops": fl * len(rs) / pre_s / 1e12,
+                "prefill_frac_of_bf16_peak": fl * len(rs) / pre_s / 1e12 / peaks["bf16_tflops"],
+                "decode_hbm_gbs": by / (dec_s / ntok) / 1e9, "decode_roofline_frac": by / (dec_s / ntok) / 1e9 / peaks["hbm_gbs"],
+                "algorithmic_bytes_per_step": by, "prefill_flop": fl, "e2e_tok_s": ntok / sum(r[0] for r in rs), "gpu_launches": int(launches)}
+
+    only = os.environ.get("CRANE_B200_BENCH_ONLY", "")          # "nifarax" / "closest": one side only (launch lists, profiles)
+    variants = {}
+    sampler.start()
+    for name, pair in sizes.items():
+        variants[name] = {}
+        for key, cls in (("nifarax", crane_b200.NifaraxModel), ("closest_model_fosovik", crane_b200.FosovikModel)):
+            if only and not key.startswith(only):
+                continue
+            cfg = pair["nif" if key == "nifarax" else "fsv"]
+            m = load(cls, cfg)
+            variants[name][key] = measure(m, cfg, name + key)
+            m.close()
+        if only:
+            break
+    clocks = sampler.summary()
+    first = variants["w1024_12layers_8x896_top4"]
+    d = first.get("nifarax") or first["closest_model_fosovik"]
+    out = {"metric": "decode_tok_per_s", "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": f"Nifarax layer-list decoder (width 1024, 8 latent-attention + 4 gated-linear-attention layers, 8 experts x 896 + shared), {S}-token prefill + {n_dec} greedy decode tokens per request; the closest existing model at equal size beside it",
+                      "weights": "random bf16 blocks (timing only)", "l2": "per-token weight stream > 126 MB L2", "parallelism": "1 GPU",
+                      "precision": os.environ.get("CRANE_B200_PRECISION", "split")},
+           "value": d["decode_tok_s"], "ms_per_step": 1e3 / d["e2e_tok_s"] * n_dec, "prefill_ms": d["prefill_ms"], "prefill_tflops": d["prefill_tflops"],
+           "e2e": {"value": d["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": int(S * 4), "d2h_bytes_per_step": int((n_dec + 1) * 4),
+                   "api": "crane_b200_generate_greedy (host prompt ids in, host token ids out; prefill inside the timed region)"},
+           "gpu_launches": d["gpu_launches"], "clocks": clocks, "variants": variants,
+           "roofline": {"bound": "hbm", "achieved": d["decode_hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d["decode_roofline_frac"],
+                        "peak_source": peaks["source"], "launch": "one decode step (graph replay): the token's weights once + cached latent rows + recurrent states"}}
+    print(json.dumps(out))
+
+
 def other_config_summary(config, steps=2, timeout_s=120):
     """One more BASELINE config measured by THIS script in a child process (`bench.py --config <config>`), condensed for the headline
     line's `other_configs` field.  A child, so that nothing it does -- a failure, a hang (killed at the timeout) -- can keep the
@@ -598,7 +727,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="crane_b200", choices=["crane_b200", "reference"])
-    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b", "fosovik", "gavipel"])
+    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b", "fosovik", "gavipel", "nifarax"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the config-2 (Qwen3.5-0.8B) child measurement appended to the headline line")
     args = ap.parse_args()
@@ -614,6 +743,8 @@ def main():
         return bench_fosovik(args, rank, world, local_rank)
     if args.config == "gavipel":
         return bench_gavipel(args, rank, world, local_rank)
+    if args.config == "nifarax":
+        return bench_nifarax(args, rank, world, local_rank)
     cfg = synth.QWEN3_VL_2B if args.config == "qwen3_vl_2b" else synth.TINY_QWEN3_VL
     name = "Qwen3-VL-2B" if args.config == "qwen3_vl_2b" else "tiny-Qwen3-VL"
     workload = f"{name} bf16, 1x(448x448) image + {N_TEXT}-tok prompt, prefill + {N_DECODE} greedy decode tokens per request"

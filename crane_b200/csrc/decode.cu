@@ -212,7 +212,11 @@ gemv_kernel(GemvArgs a) {
             for (int b = 0; b < B; ++b) {
                 const float v = acc_s[(size_t)b * rpc + i] * (NORM ? rstd_s[b] : 1.f);
                 float* yp = a.y + (size_t)b * a.ldy + r0 + i;
-                if constexpr (EPI == GEMV_RESID) *yp += a.out_scale ? a.out_scale[r0 + i] * v : v; else *yp = v;
+                if constexpr (EPI == GEMV_RESID) {
+                    float add = a.out_scale ? a.out_scale[r0 + i] * v : v;
+                    if (a.gate) add *= 1.f / (1.f + expf(-(a.gate[(size_t)b * a.ldg + r0 + i] + (a.gate_bias ? a.gate_bias[r0 + i] : 0.f))));
+                    *yp += add;
+                } else *yp = v;
                 if constexpr (EPI == GEMV_LOGITS_ARGMAX) {
                     if (v > bestv[b]) { bestv[b] = v; besti[b] = r0 + i; }   // a thread's rows ascend: first maximum wins
                 }

@@ -61,6 +61,9 @@ struct GemvArgs {
     float glu_limit;        // GEMV_SILU_MUL: 0 = SiLU(gate) * up; > 0 = the clamped gated unit with this limit (common.cuh glu_pair_f)
     int norm_dim;           // NORM kernels: the mean of squares divides by this many columns (0: K) -- a K padded with zero columns
     const float* out_scale; // GEMV_RESID, nullable [N]: y[n] += out_scale[n] * (W x)[n]
+    const float* gate;      // GEMV_RESID, nullable [B, ldg]: the added value is multiplied by sigmoid(gate[b, n] + gate_bias[n]) (gate_bias nullable)
+    int ldg;
+    const float* gate_bias;
     const uint32_t* force_tokens;  // optional [out_stride]: teacher forcing -- token fed back at step s is force_tokens[s] (argmax still reported)
 };
 

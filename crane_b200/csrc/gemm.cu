@@ -143,6 +143,15 @@ __device__ __forceinline__ void epi_block(const GemmEpi& ep, uint8_t* stg, int m
             v[j] *= c.x; v[j + 1] *= c.y; v[j + 2] *= c.z; v[j + 3] *= c.w;
         }
     }
+    if (ep.gate != nullptr && m_base + lane < M) {      // a lane holds 32 neighbouring columns of its own row
+        const float* g = ep.gate + (size_t)(m_base + lane) * ep.ldg + n;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            float4 z = *reinterpret_cast<const float4*>(g + j);
+            if (ep.gate_bias != nullptr) { const float4 b = *reinterpret_cast<const float4*>(ep.gate_bias + n + j); z.x += b.x; z.y += b.y; z.z += b.z; z.w += b.w; }
+            v[j] *= 1.f / (1.f + expf(-z.x)); v[j + 1] *= 1.f / (1.f + expf(-z.y)); v[j + 2] *= 1.f / (1.f + expf(-z.z)); v[j + 3] *= 1.f / (1.f + expf(-z.w));
+        }
+    }
     if constexpr (MODE == EPI_STORE_F32 || MODE == EPI_RESID_F32) {
         uint8_t* mine = stg + lane * EPI_PITCH;
         // the residual rows first (independent loads, all in flight together), then the transpose
@@ -465,6 +474,8 @@ gemm_simt_kernel(const bf16* __restrict__ A, const bf16* __restrict__ A_lo, int 
             for (int j = 0; j < 32; ++j) acc[j] += ep.bias[n0 + j];
         if (ep.col_scale != nullptr)
             for (int j = 0; j < 32; ++j) acc[j] *= ep.col_scale[n0 + j];
+        if (ep.gate != nullptr)
+            for (int j = 0; j < 32; ++j) acc[j] *= 1.f / (1.f + expf(-(ep.gate[(size_t)m * ep.ldg + n0 + j] + (ep.gate_bias ? ep.gate_bias[n0 + j] : 0.f))));
         epi_store32<MODE>(ep, m, n0, acc, true);
     }
 }

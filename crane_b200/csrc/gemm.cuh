@@ -34,6 +34,8 @@ struct GemmEpi {
     int mode;
     bool w_dynamic = false;   // W was written by an earlier kernel of the chain (dequantised scratch): no weight prefetch before the dependency wait
     const float* col_scale = nullptr;   // [N] or nullptr: the accumulator (+ bias) of column n is multiplied by col_scale[n] before the mode's store / add
+    const float* gate = nullptr; int ldg = 0; const float* gate_bias = nullptr;   // nullable [M, ldg] (+ [N]): the accumulator of (m, n) is multiplied by
+                                        // sigmoid(gate[m, n] + gate_bias[n]) after bias and col_scale, before the mode's store / add
     float glu_limit = 0.f;    // EPI_SILU_MUL_BF16 only: 0 = SiLU(gate) * up; > 0 = the clamped gated unit with this limit
     unsigned long long* prof = nullptr;   // optional: 8 globaltimer stamps per CTA (tile timeline, tools/gemm_probe.py)
 };

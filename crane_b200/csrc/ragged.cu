@@ -72,7 +72,8 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, int lds, const
 // 64 x 64 output tile, 16-wide k-steps, 256 threads x (4 x 4) accumulators; each output element sums k = 0 .. K-1 in order.
 template <int MODE>
 __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict__ A, int lda, const bf16* __restrict__ Wt, int ldw, int M, int N,
-                                                         int K, float* __restrict__ C, int ldc, const float* __restrict__ col_scale) {
+                                                         int K, float* __restrict__ C, int ldc, const float* __restrict__ col_scale,
+                                                         const float* __restrict__ gate, int ldg, const float* __restrict__ gate_bias) {
     __shared__ float sa[16][64 + 4], sw[16][64 + 4];
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     float acc[4][4] = {};
@@ -102,7 +103,10 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
             const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
             if (m < M && n < N) {
                 float* p = C + (size_t)m * ldc + n;
-                *p = (MODE == LIN_RESID) ? *p + (col_scale ? col_scale[n] * acc[i][j] : acc[i][j]) : acc[i][j];
+                float v = acc[i][j];
+                if (MODE == LIN_RESID && col_scale) v *= col_scale[n];
+                if (MODE == LIN_RESID && gate) v *= 1.f / (1.f + expf(-(gate[(size_t)m * ldg + n] + (gate_bias ? gate_bias[n] : 0.f))));
+                *p = (MODE == LIN_RESID) ? *p + v : v;
             }
         }
 }
@@ -138,7 +142,7 @@ __global__ void attn_prep_kernel(RaggedBatch rb, AttnPrepArgs a) {
             float ss = 0.f;
             for (int c = lane; c < a.d; c += 32) ss += src[c] * src[c];
             ss = warp_sum(ss);
-            const float inv = 1.f / sqrtf(ss / (float)a.d + a.eps) * (isq ? temp : 1.f);
+            const float inv = a.no_norm ? 1.f : 1.f / sqrtf(ss / (float)a.d + a.eps) * (isq ? temp : 1.f);
             KT* dst = nullptr;
             if (!isq) dst = (KT*)a.k_pool + (((size_t)page * a.G + (hh - a.H)) * KV_PAGE + (pos % KV_PAGE)) * a.d;
             // a lane owns the pairs (2i, 2i + 1), i = lane, lane + 32, ...: both halves of a rotated pair are in one thread
@@ -221,13 +225,15 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
     // 32 value rows, every plane -- into its own shared-memory patch with one burst of cp.async, so the tile costs one trip to memory
     // instead of a dozen dependent load rounds; rows are padded by 16 bytes, which spreads a lane-per-row access over all banks.
     // The arithmetic and its order are the same either way.
+    // kv_shared (one pool serves as keys and as values, d == dv): the staged key rows are the value rows too -- one copy, half the patch.
+    const bool one_copy = stage && a.kv_shared;
     const int ks_e = stage ? d + 16 / (int)sizeof(KT) : d, vs_e = stage ? dv + 16 / (int)sizeof(KT) : dv;      // row strides (elements)
     const int planes = (sizeof(KT) == 2 && a.kv_lo_off) ? 2 : 1;
     KT* kst = nullptr; KT* vst = nullptr;
     if (stage) {
         KT* all = reinterpret_cast<KT*>(wa + (size_t)ATT_WARPS * REP * dv + ((4 - ((REP * d + 2 * ATT_WARPS * REP + ATT_WARPS * REP * dv) & 3)) & 3));
-        kst = all + (size_t)warp * 32 * planes * (ks_e + vs_e);
-        vst = kst + (size_t)32 * planes * ks_e;
+        kst = all + (size_t)warp * 32 * planes * (one_copy ? ks_e : ks_e + vs_e);
+        vst = one_copy ? kst : kst + (size_t)32 * planes * ks_e;
     }
     const long long klo = !stage ? a.kv_lo_off : planes == 2 ? (long long)32 * ks_e : 0, vlo = !stage ? a.kv_lo_off : planes == 2 ? (long long)32 * vs_e : 0;
     for (int t = t_lo + warp; t < t_hi; t += ATT_WARPS) {
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
                     cp_async16s(reinterpret_cast<unsigned char*>(kst + (size_t)pl * 32 * ks_e + (size_t)row * ks_e) + ch * 16,
                                 reinterpret_cast<const unsigned char*>(ksrc + (size_t)row * d) + ch * 16);
                 }
-                for (int i = lane; i < cnt * vc; i += 32) {
+                for (int i = lane; i < (one_copy ? 0 : cnt * vc); i += 32) {
                     const int row = i / vc, ch = i % vc;
                     cp_async16s(reinterpret_cast<unsigned char*>(vst + (size_t)pl * 32 * vs_e + (size_t)row * vs_e) + ch * 16,
                                 reinterpret_cast<const unsigned char*>(vsrc + (size_t)row * dv) + ch * 16);
@@ -983,11 +989,11 @@ int gather_rows_launch(cudaStream_t st, const float* src, int lds, const int* ro
     return last_err();
 }
 int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc,
-                      const float* col_scale) {
+                      const float* col_scale, const float* gate, int ldg, const float* gate_bias) {
     if (M <= 0 || N <= 0 || K <= 0) return -1000;
     const dim3 grid((N + 63) / 64, (M + 63) / 64);
-    if (mode == LIN_RESID) linear_f32_kernel<LIN_RESID><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc, col_scale);
-    else linear_f32_kernel<LIN_STORE><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc, nullptr);
+    if (mode == LIN_RESID) linear_f32_kernel<LIN_RESID><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc, col_scale, gate, ldg, gate_bias);
+    else linear_f32_kernel<LIN_STORE><<<grid, 256, 0, st>>>(A, lda, W, ldw, M, N, K, C, ldc, nullptr, nullptr, 0, nullptr);
     return last_err();
 }
 int rms_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, float eps, const float* w1, const ActOut& out1,
@@ -1018,7 +1024,7 @@ static int sink_attention_launch_t(cudaStream_t st, const RaggedBatch& rb, const
     if (smem > 200 * 1024) return -1000;
     // per-warp staging patches for the key / value tiles where the widths allow 16-byte copies and the patches fit
     const int planes = (sizeof(KT) == 2 && a.kv_lo_off) ? 2 : 1;
-    const size_t patch = (size_t)ATT_WARPS * 32 * planes * ((size_t)a.d * sizeof(KT) + 16 + (size_t)a.dv * sizeof(KT) + 16) + 16;
+    const size_t patch = (size_t)ATT_WARPS * 32 * planes * ((size_t)a.d * sizeof(KT) + 16 + (a.kv_shared ? 0 : (size_t)a.dv * sizeof(KT) + 16)) + 16;
     // ... and the launch is small (a decode step: about two blocks per SM at most).  A launch of thousands of blocks hides its load
     // latency by residency instead, which the patches' shared memory would take away.
     const int stage = ((a.d & 7) == 0 && (a.dv & 7) == 0 && smem + patch <= 200 * 1024 && (long long)rb.T * a.G * nb * a.nsplit <= 300) ? 1 : 0;
@@ -1044,6 +1050,7 @@ static int sink_attention_launch_k(cudaStream_t st, const RaggedBatch& rb, const
 }
 int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a) {
     if (a.dv > 32 * ATT_MAXC || a.H % a.G) return -1000;
+    if (a.kv_shared && (a.k_pool != a.v_pool || a.d != a.dv)) return -1000;
     int e = a.kv_f32 ? sink_attention_launch_k<float>(st, rb, a) : sink_attention_launch_k<bf16>(st, rb, a);
     if (e || a.nsplit == 1) return e;
     if (a.nsplit > 64) return -1000;

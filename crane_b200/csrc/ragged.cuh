@@ -44,9 +44,10 @@ int rms_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, i
 // dst[r, col0 + c] = src[r, c] for c < W, in every form dst carries (f32 rows, bf16 planes)
 int store_rows_launch(cudaStream_t st, const float* src, int lds, int T, int W, const ActOut& dst, int col0);
 // C[M, N] (+)= A[M, K] f32 x W[N, K]^T bf16, every product and sum in f32 (no tensor cores): the exact mode's linear, and the router's.
-// col_scale (LIN_RESID only, nullable): C[m, n] += col_scale[n] * acc
+// col_scale (LIN_RESID only, nullable): C[m, n] += col_scale[n] * acc;  gate (LIN_RESID only, nullable [M, ldg], gate_bias nullable [N]):
+// the added value is also multiplied by sigmoid(gate[m, n] + gate_bias[n])
 int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc,
-                      const float* col_scale = nullptr);
+                      const float* col_scale = nullptr, const float* gate = nullptr, int ldg = 0, const float* gate_bias = nullptr);
 // out[r, j] = silu(gu[r, 2j]) * gu[r, 2j + 1]  (interleaved (gate, up) pairs)
 int silu_glu_launch(cudaStream_t st, const float* gu, int ld, int T, int F, const ActOut& out);
 
@@ -64,6 +65,7 @@ struct AttnPrepArgs {
     int kv_f32; long long kv_lo_off;  // bf16 pages: element offset of the plane holding bf16(x - bf16(x)), 0 = none
     int has_kv;
     const int* block_table; int max_pages;
+    int no_norm = 0;                  // 1: queries and keys pass as they are (no RMS norm, no temperature); rotation still applies
 };
 int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs& a);
 
@@ -78,6 +80,7 @@ struct SinkAttnArgs {
     const float* gate; int ldg;       // nullable [T, ldg]: out[r, h * dv + c] *= sigmoid(gate[r, h * dv + c])
     ActOut out;                       // [T, H * dv]
     float* part; int nsplit;          // scratch [T, H, nsplit, dv + 2] when nsplit > 1
+    int kv_shared = 0;                // 1: k_pool == v_pool and d == dv -- a cached row is its own value (staged once)
 };
 int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a);
 
@@ -163,6 +166,10 @@ struct CausalConvArgs {
 int causal_conv_launch(cudaStream_t st, const RaggedBatch& rb, const CausalConvArgs& a);
 int causal_conv_launch_count(const CausalConvArgs& a);
 
+// Every entry one row: out_h = rms_in_groups(x) * norm_w, out_u = out_h + conv(out_h) over the carried window, window moved on -- one launch
+int norm_conv_step_launch(cudaStream_t st, const RaggedBatch& rb, const float* x, int ldx, int W, int groups, float eps, const float* norm_w,
+                          int taps, const float* conv_w, float* state, const ActOut& out_h, const ActOut& out_u);
+
 // x[r, c] += sigmoid(gate[r, c] + bias[c]) * y[r, c]
 int gated_add_launch(cudaStream_t st, float* x, int ldx, const float* y, int ldy, const float* gate, int ldg, const float* bias, int T, int W);
 
@@ -175,6 +182,7 @@ struct LatentPrepArgs {
     const float* q_w; const float* kv_w;
     float eps;
     ActOut cq;
+    ActOut ckv;                       // optional: the normalised key / value latent of the step's rows, as an operand for further linears
     void* pool; int kv_f32; long long kv_lo_off;
     const int* block_table; int max_pages;
 };
@@ -190,7 +198,7 @@ int headwise_linear_launch(cudaStream_t st, const ActOut& in, const bf16* w, int
 struct GlaArgs {
     const float* proj; int ld;
     int H, d, dv, rank;
-    const float* a2;                  // [H * d, rank] f32
+    const float* a2;                  // [rank, H * d] f32 (the second factor of the decay's projection, transposed)
     const float* a2_b;                // [H * d]
     float inv_tau, q_scale, eps;
     const float* norm_w;              // [dv]

@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(RaggedBatch rb, Latent
         const float inv = 1.f / sqrtf(tot / (float)n + a.eps);
         for (int c = threadIdx.x; c < n; c += 256) {
             const float v = src[c] * inv * w[c];
-            if (seg) kv_store<KT>(dst + c, v, a.kv_lo_off);
+            if (seg) { kv_store<KT>(dst + c, v, a.kv_lo_off); if (a.ckv.f || a.ckv.hi) store_act(a.ckv, r, c, v); }
             else store_act(a.cq, r, c, v);
         }
     }
@@ -137,20 +137,103 @@ __global__ void __launch_bounds__(128) headwise_linear_kernel(ActOut in, const b
     }
 }
 
+// Up to HWF_ROWS rows (a decode step): block = (64 output columns, head); its four warps split the head's n_in input rows between them,
+// a lane owns two neighbouring columns (one 4-byte load of the bf16 weights per input row, the warp reads 128 contiguous bytes), and
+// the warps' partial sums meet in warp order.
+constexpr int HWF_ROWS = 4;
+__global__ void __launch_bounds__(128) headwise_few_kernel(ActOut in, const bf16* __restrict__ w, int T, int n_in, int n_out, ActOut out) {
+    extern __shared__ float hwf_s[];                      // [T][n_in] inputs, then [4 warps][HWF_ROWS][64] partial sums
+    float* xin = hwf_s;
+    float* part = hwf_s + (size_t)T * n_in;
+    const int h = blockIdx.y, c0 = blockIdx.x * 64, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < T * n_in; i += blockDim.x) { const int rr = i / n_in, j = i - rr * n_in; xin[i] = act_load(in, rr, h * n_in + j); }
+    __syncthreads();
+    const int col = c0 + 2 * lane, per = (n_in + 3) / 4, j0 = warp * per, j1 = min(n_in, j0 + per);
+    const bool two = col + 1 < n_out && (n_out & 1) == 0;  // (an even width keeps every pair 4-byte aligned)
+    float acc[HWF_ROWS][2] = {};
+    if (col < n_out) {
+        const bf16* wh = w + (size_t)h * n_in * n_out + col;
+#pragma unroll 4
+        for (int j = j0; j < j1; ++j) {
+            float w0, w1 = 0.f;
+            if (two) { const uint32_t u = *reinterpret_cast<const uint32_t*>(wh + (size_t)j * n_out); w0 = bf16lo(u); w1 = bf16hi(u); }
+            else { w0 = __bfloat162float(wh[(size_t)j * n_out]); if (col + 1 < n_out) w1 = __bfloat162float(wh[(size_t)j * n_out + 1]); }
+#pragma unroll
+            for (int rr = 0; rr < HWF_ROWS; ++rr) if (rr < T) { const float xv = xin[rr * n_in + j]; acc[rr][0] = fmaf(xv, w0, acc[rr][0]); acc[rr][1] = fmaf(xv, w1, acc[rr][1]); }
+        }
+    }
+#pragma unroll
+    for (int rr = 0; rr < HWF_ROWS; ++rr) { part[(warp * HWF_ROWS + rr) * 64 + 2 * lane] = acc[rr][0]; part[(warp * HWF_ROWS + rr) * 64 + 2 * lane + 1] = acc[rr][1]; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < T * 64; i += blockDim.x) {
+        const int rr = i >> 6, c = i & 63;
+        if (c0 + c < n_out) store_act(out, rr, h * n_out + c0 + c, ((part[rr * 64 + c] + part[(HWF_ROWS + rr) * 64 + c]) + part[(2 * HWF_ROWS + rr) * 64 + c]) + part[(3 * HWF_ROWS + rr) * 64 + c]);
+    }
+}
+
+// Every entry one token: the sublayer's norm (RMS in equal groups), the convolution over the carried window and the window's shift
+// in one pass.  Block per entry; h = norm output goes to out_h, h + conv(h) to out_u.
+__global__ void __launch_bounds__(256) norm_conv_step_kernel(RaggedBatch rb, const float* __restrict__ x, int ldx, int W, int groups, float eps,
+                                                             const float* __restrict__ nw, int taps, const float* __restrict__ cw, float* state,
+                                                             ActOut out_h, ActOut out_u) {
+    __shared__ float red[8];
+    const int e = blockIdx.x, r = rb.ent_row0[e], slot = rb.ent_slot[e], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* xr = x + (size_t)r * ldx;
+    float* win = state + (size_t)slot * (taps - 1) * W;
+    const int part = W / groups;
+    for (int g = 0; g < groups; ++g) {
+        const int c0 = g * part;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < part; c += 256) ss = fmaf(xr[c0 + c], xr[c0 + c], ss);
+        ss = warp_sum(ss);
+        if (g) __syncthreads();
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tot += red[k];
+        const float inv = 1.f / sqrtf(tot / (float)part + eps);
+        for (int c = c0 + threadIdx.x; c < c0 + part; c += 256) {
+            const float u = xr[c] * inv * nw[c];
+            float acc = 0.f;
+            for (int k = 0; k < taps - 1; ++k) {
+                const float wv = win[(size_t)k * W + c];
+                acc = fmaf(cw[(size_t)c * taps + k], wv, acc);
+                if (k > 0) win[(size_t)(k - 1) * W + c] = wv;
+            }
+            acc = fmaf(cw[(size_t)c * taps + taps - 1], u, acc);
+            if (taps > 1) win[(size_t)(taps - 2) * W + c] = u;
+            store_act(out_h, r, c, u);
+            store_act(out_u, r, c, u + acc);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------- gated linear attention
 // decay[r, c] = sigmoid(z)^(1 / tau) = exp(log_sigmoid(z) / tau), z = a2[c, :] . a[r, :] + b[c]; log_sigmoid(z) = min(z, 0) - log1p(e^-|z|)
-__global__ void __launch_bounds__(256) gla_decay_kernel(GlaArgs a) {
-    extern __shared__ float lowrank[];                    // [rank]
-    const int r = blockIdx.x, C = a.H * a.d;
-    const float* src = a.proj + (size_t)r * a.ld + 2 * C + 2 * a.H * a.dv;
-    for (int j = threadIdx.x; j < a.rank; j += blockDim.x) lowrank[j] = src[j];
+// (a2 is stored transposed, [rank, H * d]: neighbouring threads read neighbouring channels; GLA_DROWS rows share each weight)
+constexpr int GLA_DROWS = 8;
+__global__ void __launch_bounds__(256) gla_decay_kernel(GlaArgs a, int T) {
+    extern __shared__ float lowrank[];                    // [GLA_DROWS][rank]
+    const int r0 = blockIdx.x * GLA_DROWS, C = a.H * a.d, nr = min(GLA_DROWS, T - r0);
+    for (int i = threadIdx.x; i < GLA_DROWS * a.rank; i += blockDim.x) {
+        const int rr = i / a.rank, j = i - rr * a.rank;
+        lowrank[i] = rr < nr ? a.proj[(size_t)(r0 + rr) * a.ld + 2 * C + 2 * a.H * a.dv + j] : 0.f;
+    }
     __syncthreads();
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float z = a.a2_b[c];
-        const float* row = a.a2 + (size_t)c * a.rank;
-        for (int j = 0; j < a.rank; ++j) z = fmaf(row[j], lowrank[j], z);
-        const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-        a.decay[(size_t)r * C + c] = expf(ls * a.inv_tau);
+        float z[GLA_DROWS];
+        const float b = a.a2_b[c];
+#pragma unroll
+        for (int rr = 0; rr < GLA_DROWS; ++rr) z[rr] = b;
+        for (int j = 0; j < a.rank; ++j) {
+            const float wv = a.a2[(size_t)j * C + c];
+#pragma unroll
+            for (int rr = 0; rr < GLA_DROWS; ++rr) z[rr] = fmaf(wv, lowrank[rr * a.rank + j], z[rr]);
+        }
+#pragma unroll
+        for (int rr = 0; rr < GLA_DROWS; ++rr)
+            if (rr < nr) a.decay[(size_t)(r0 + rr) * C + c] = expf((fminf(z[rr], 0.f) - log1pf(expf(-fabsf(z[rr])))) * a.inv_tau);
     }
 }
 
@@ -286,6 +369,12 @@ int causal_conv_launch(cudaStream_t st, const RaggedBatch& rb, const CausalConvA
     if (a.taps > 1) causal_conv_window_kernel<<<dim3((a.C + 127) / 128, rb.E), 128, 0, st>>>(rb, a);
     return last_err();
 }
+int norm_conv_step_launch(cudaStream_t st, const RaggedBatch& rb, const float* x, int ldx, int W, int groups, float eps, const float* norm_w,
+                          int taps, const float* conv_w, float* state, const ActOut& out_h, const ActOut& out_u) {
+    if (groups < 1 || W % groups || taps < 1) return -1000;
+    norm_conv_step_kernel<<<rb.E, 256, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, taps, conv_w, state, out_h, out_u);
+    return last_err();
+}
 int gated_add_launch(cudaStream_t st, float* x, int ldx, const float* y, int ldy, const float* gate, int ldg, const float* bias, int T, int W) {
     gated_add_kernel<<<dim3((W + 127) / 128, T), 128, 0, st>>>(x, ldx, y, ldy, gate, ldg, bias, W);
     return last_err();
@@ -303,6 +392,13 @@ int latent_prep_launch(cudaStream_t st, const RaggedBatch& rb, const LatentPrepA
 int headwise_linear_launch(cudaStream_t st, const ActOut& in, const bf16* w, int T, int H, int n_in, int n_out, const ActOut& out) {
     const size_t smem = (size_t)HW_ROWS * n_in * sizeof(float);
     if ((!in.f && !in.hi) || smem > 200 * 1024) return -1000;
+    if (T <= HWF_ROWS) {
+        const size_t sf = ((size_t)T * n_in + 4 * HWF_ROWS * 64) * sizeof(float);
+        static SmemOptIn seen_few;
+        if (const int e = ensure_dyn_smem(headwise_few_kernel, sf, seen_few)) return e;
+        headwise_few_kernel<<<dim3((n_out + 63) / 64, H), 128, sf, st>>>(in, w, T, n_in, n_out, out);
+        return last_err();
+    }
     static SmemOptIn seen;
     if (const int e = ensure_dyn_smem(headwise_linear_kernel, smem, seen)) return e;
     headwise_linear_kernel<<<dim3((T + HW_ROWS - 1) / HW_ROWS, H), 128, smem, st>>>(in, w, T, n_in, n_out, out);
@@ -310,7 +406,7 @@ int headwise_linear_launch(cudaStream_t st, const ActOut& in, const bf16* w, int
 }
 int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a) {
     if (a.d < 1 || a.d > 256 || a.dv < 1 || a.rank < 1 || a.rank > 8192) return -1000;
-    gla_decay_kernel<<<rb.T, 256, (size_t)a.rank * sizeof(float), st>>>(a);
+    gla_decay_kernel<<<(rb.T + GLA_DROWS - 1) / GLA_DROWS, 256, (size_t)GLA_DROWS * a.rank * sizeof(float), st>>>(a, rb.T);
     int e = last_err();
     if (e) return e;
     const int nr = (a.d + GLA_NS - 1) / GLA_NS, R = nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
