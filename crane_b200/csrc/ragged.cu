@@ -1106,6 +1106,9 @@ int clamped_glu_launch(cudaStream_t st, const float* gu, int ld, int stride, int
     clamped_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, stride, up_off, F, limit, out);
     return last_err();
 }
+static bool moe_few_pairs(const MoeArgs& a) {
+    return a.T * a.top <= 32 && (a.ldwu & 255) == 0 && (a.ldwd & 255) == 0 && (size_t)std::max(a.ldwu, a.ldwd) * 4 <= 48 * 1024;
+}
 int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, int ldw) {
     if (a.E > 256 || a.top > a.E || a.top < 1) return -1000;
     if (a.n_groups > 1 && (a.E % a.n_groups || a.keep < 1 || a.keep > a.n_groups || a.top > a.keep * (a.E / a.n_groups))) return -1000;
@@ -1119,12 +1122,12 @@ int moe_route_launch(cudaStream_t st, const MoeArgs& a, const bf16* w_router, in
         route_kernel<<<(a.T + 3) / 4, 128, 0, st>>>(a);
         e = last_err();
     }
-    if (e) return e;
+    if (e || moe_few_pairs(a)) return e;                  // (a handful of pairs go through moe_gemv, which reads the choices as they are)
     moe_sort_kernel<<<1, 1024, (size_t)3 * a.E * sizeof(int), st>>>(a);
     return last_err();
 }
 int moe_experts_launch(cudaStream_t st, const MoeArgs& a) {
-    if (a.T * a.top <= 32 && (a.ldwu & 255) == 0 && (a.ldwd & 255) == 0 && (size_t)std::max(a.ldwu, a.ldwd) * 4 <= 48 * 1024) {
+    if (moe_few_pairs(a)) {
         moe_gemv_kernel<true><<<dim3(((a.gated ? 2 * a.F : a.F) + 15) / 16, a.T * a.top), 256, (size_t)a.ldwu * 4, st>>>(a);
         int e = last_err();
         if (e) return e;

@@ -206,9 +206,15 @@ struct GlaArgs {
     float* decay;                     // [T, H * d] scratch
     float* y;                         // [T, H * dv] scratch
     ActOut out;                       // [T, H * dv]
+    // long portions run as segments side by side (see gla_scan_kernel): scratch for their local / start states and decay products,
+    // gla_seg_floats(entries, ...) floats in all; nullptr = never segment
+    float* seg_state = nullptr; float* seg_decay = nullptr;
+    int max_len = 0;                  // rows of the longest entry
 };
 int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a);
-constexpr int GLA_LAUNCHES = 3;
+int gla_launch_count(bool has_seg_scratch, int max_len);
+size_t gla_seg_floats(int entries, int H, int d, int dv);
+size_t gla_seg_decay_offset(int entries, int H, int d, int dv);
 
 // dst[r, c] = cap * tanh(src[r, c] / cap) for c < V (cap <= 0: a plain copy)
 int softcap_rows_launch(cudaStream_t st, const float* src, int lds, int R, int V, float cap, float* dst, int ldd);

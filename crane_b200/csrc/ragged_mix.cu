@@ -245,24 +245,39 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(GlaArgs a, int T) {
 constexpr int GLA_NS = 8, GLA_COLS = 16, GLA_CH = 16;
 __host__ __device__ inline int gla_idx(int n, int R) { return n + 4 * (n / R); }
 __host__ __device__ inline int gla_npad(int R) { return 8 * (R + 4); }
-template <int R>
+// Long portions are cut into GLA_SEGS segments that run side by side (one resident warp per scheduler waits on its own dependent
+// chain most of the time): the recurrence is linear with a decay per state ROW, so
+//   S_end(segment) = diag(product of the segment's decays) * S_start + S_local(segment run from zero).
+// MODE 1 runs every segment from zero and leaves S_local and the decay products; gla_seg_prefix_kernel turns them into each segment's
+// start state (and the sequence's new state); MODE 2 is the scan proper from those start states.  MODE 0 = one segment, everything.
+constexpr int GLA_SEGS = 4, GLA_SEG_MIN = 512;
+__host__ __device__ inline int gla_seg_len(int len) { return ((len + GLA_SEGS - 1) / GLA_SEGS + GLA_CH - 1) / GLA_CH * GLA_CH; }
+template <int R, int MODE>
 __global__ void __launch_bounds__(GLA_COLS * GLA_NS) gla_scan_kernel(RaggedBatch rb, GlaArgs a) {
     extern __shared__ __align__(16) float gla_s[];
-    const int e = blockIdx.x, h = blockIdx.y, ns = threadIdx.x & (GLA_NS - 1), pl = threadIdx.x / GLA_NS;
+    const int e = MODE == 0 ? blockIdx.x : blockIdx.x / GLA_SEGS, seg = MODE == 0 ? 0 : blockIdx.x % GLA_SEGS;
+    const int h = blockIdx.y, ns = threadIdx.x & (GLA_NS - 1), pl = threadIdx.x / GLA_NS;
     const int p0 = blockIdx.z * GLA_COLS, p = p0 + pl;
     const int d = a.d, dv = a.dv, C = a.H * d;
     const bool live = p < dv;
-    const int len = rb.ent_len[e], slot = rb.ent_slot[e], r0 = rb.ent_row0[e];
+    const int full_len = rb.ent_len[e], slot = rb.ent_slot[e];
+    const int seg_len = MODE == 0 ? full_len : gla_seg_len(full_len), seg0 = seg * seg_len;
+    if (seg0 >= full_len) return;                             // (a short entry has fewer segments)
+    const int len = min(seg_len, full_len - seg0), r0 = rb.ent_row0[e] + seg0;
     const int ncol = min(GLA_COLS, dv - p0);
     const int NP = gla_npad(R), per_tok = GLA_COLS + 3 * NP;
     float* stage[2] = {gla_s, gla_s + GLA_CH * per_tok};
-    float* S = a.state + (((size_t)slot * a.H + h) * d) * dv;
+    float* S = MODE == 0 ? a.state + (((size_t)slot * a.H + h) * d) * dv : a.seg_state + ((((size_t)e * GLA_SEGS + seg) * a.H + h) * d) * dv;
     const int n0 = ns * R;
     for (int i = threadIdx.x; i < 2 * GLA_CH * per_tok; i += blockDim.x) gla_s[i] = 0.f;
     __syncthreads();
-    float s[R];
+    float s[R], dprod[MODE == 1 ? R : 1];
 #pragma unroll
-    for (int i = 0; i < R; ++i) s[i] = (n0 + i < d && live) ? S[(size_t)(n0 + i) * dv + p] : 0.f;
+    for (int i = 0; i < R; ++i) s[i] = (MODE != 1 && n0 + i < d && live) ? S[(size_t)(n0 + i) * dv + p] : 0.f;
+    if constexpr (MODE == 1) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) dprod[i] = 1.f;
+    }
     const int qoff = h * d, koff = C + h * d, voff = 2 * C + h * dv + p0;
     // 16-byte copies when every piece starts on a 16-byte boundary (the usual geometry), 4-byte copies otherwise
     const bool wide = ((d | dv | a.ld | C) & 3) == 0 && (R & 3) == 0;
@@ -319,6 +334,16 @@ __global__ void __launch_bounds__(GLA_COLS * GLA_NS) gla_scan_kernel(RaggedBatch
                 const float4* K4 = reinterpret_cast<const float4*>(kp);
                 const float4* Q4 = reinterpret_cast<const float4*>(kp + NP);
                 const float4* A4 = reinterpret_cast<const float4*>(kp + 2 * NP);
+                if constexpr (MODE == 1) {                    // state and decay products only
+#pragma unroll
+                    for (int i = 0; i < R / 4; ++i) {
+                        const float4 k = K4[i], al = A4[i];
+                        s[4 * i]     = fmaf(al.x, s[4 * i],     k.x * xv); s[4 * i + 1] = fmaf(al.y, s[4 * i + 1], k.y * xv);
+                        s[4 * i + 2] = fmaf(al.z, s[4 * i + 2], k.z * xv); s[4 * i + 3] = fmaf(al.w, s[4 * i + 3], k.w * xv);
+                        dprod[4 * i] *= al.x; dprod[4 * i + 1] *= al.y; dprod[4 * i + 2] *= al.z; dprod[4 * i + 3] *= al.w;
+                    }
+                    continue;
+                }
 #pragma unroll
                 for (int i = 0; i < R / 4; ++i) {
                     const float4 k = K4[i], q = Q4[i], al = A4[i];
@@ -335,8 +360,32 @@ __global__ void __launch_bounds__(GLA_COLS * GLA_NS) gla_scan_kernel(RaggedBatch
         }
         __syncthreads();                                      // the stage is free for chunk c + 2
     }
+    if (MODE == 2) return;                                    // the prefix kernel already wrote the sequence's new state
 #pragma unroll
     for (int i = 0; i < R; ++i) if (n0 + i < d && live) S[(size_t)(n0 + i) * dv + p] = s[i];
+    if constexpr (MODE == 1) {
+        if (pl == 0 && blockIdx.z == 0) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) if (n0 + i < d) a.seg_decay[(((size_t)e * GLA_SEGS + seg) * a.H + h) * d + n0 + i] = dprod[i];
+        }
+    }
+}
+// Start state of every segment, in order: seg_state[k] holds S_local on entry and S_start(k) on exit; the slot gets the end state.
+__global__ void gla_seg_prefix_kernel(RaggedBatch rb, GlaArgs a) {
+    const int e = blockIdx.x, h = blockIdx.y, np = a.d * a.dv;
+    const int len = rb.ent_len[e], slot = rb.ent_slot[e], nseg = (len + gla_seg_len(len) - 1) / gla_seg_len(len);
+    float* S = a.state + ((size_t)slot * a.H + h) * np;
+    for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < np; i += gridDim.z * blockDim.x) {
+        const int n = i / a.dv;
+        float cur = S[i];
+        for (int k = 0; k < nseg; ++k) {
+            float* loc = a.seg_state + (((size_t)e * GLA_SEGS + k) * a.H + h) * np + i;
+            const float l = *loc;
+            *loc = cur;
+            cur = fmaf(a.seg_decay[(((size_t)e * GLA_SEGS + k) * a.H + h) * a.d + n], cur, l);
+        }
+        S[i] = cur;
+    }
 }
 
 // out[r, h * dv + c] = y / sqrt(mean_c(y^2) + eps) * w[c] * silu(g[r, h * dv + c]): one warp per (row, head)
@@ -404,6 +453,9 @@ int headwise_linear_launch(cudaStream_t st, const ActOut& in, const bf16* w, int
     headwise_linear_kernel<<<dim3((T + HW_ROWS - 1) / HW_ROWS, H), 128, smem, st>>>(in, w, T, n_in, n_out, out);
     return last_err();
 }
+int gla_launch_count(bool has_seg_scratch, int max_len) { return has_seg_scratch && max_len >= GLA_SEG_MIN ? 5 : 3; }
+size_t gla_seg_floats(int entries, int H, int d, int dv) { return (size_t)entries * GLA_SEGS * H * ((size_t)d * dv + d); }
+size_t gla_seg_decay_offset(int entries, int H, int d, int dv) { return (size_t)entries * GLA_SEGS * H * (size_t)d * dv; }
 int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a) {
     if (a.d < 1 || a.d > 256 || a.dv < 1 || a.rank < 1 || a.rank > 8192) return -1000;
     gla_decay_kernel<<<(rb.T + GLA_DROWS - 1) / GLA_DROWS, 256, (size_t)GLA_DROWS * a.rank * sizeof(float), st>>>(a, rb.T);
@@ -412,14 +464,24 @@ int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a) {
     const int nr = (a.d + GLA_NS - 1) / GLA_NS, R = nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
     const size_t smem = (size_t)2 * GLA_CH * (GLA_COLS + 3 * gla_npad(R)) * sizeof(float);      // <= 113 KB at d = 256
     const dim3 grid(rb.E, a.H, (a.dv + GLA_COLS - 1) / GLA_COLS);
-    auto run = [&](auto kern, SmemOptIn& seen) -> int {
+    auto run = [&](auto kern, SmemOptIn& seen, dim3 g) -> int {
         if (const int er = ensure_dyn_smem(kern, smem, seen)) return er;
-        kern<<<grid, GLA_COLS * GLA_NS, smem, st>>>(rb, a);
+        kern<<<g, GLA_COLS * GLA_NS, smem, st>>>(rb, a);
         return last_err();
     };
-    static SmemOptIn seen[4];
-    e = R == 4 ? run(gla_scan_kernel<4>, seen[0]) : R == 8 ? run(gla_scan_kernel<8>, seen[1]) : R == 16 ? run(gla_scan_kernel<16>, seen[2])
-                                                                                                        : run(gla_scan_kernel<32>, seen[3]);
+    auto scan = [&](auto k4, auto k8, auto k16, auto k32, SmemOptIn* seen, dim3 g) -> int {
+        return R == 4 ? run(k4, seen[0], g) : R == 8 ? run(k8, seen[1], g) : R == 16 ? run(k16, seen[2], g) : run(k32, seen[3], g);
+    };
+    static SmemOptIn seen0[4], seen1[4], seen2[4];
+    if (gla_launch_count(a.seg_state != nullptr, a.max_len) == 3) {
+        e = scan(gla_scan_kernel<4, 0>, gla_scan_kernel<8, 0>, gla_scan_kernel<16, 0>, gla_scan_kernel<32, 0>, seen0, grid);
+    } else {
+        const dim3 ggrid(rb.E * GLA_SEGS, a.H, grid.z);
+        if ((e = scan(gla_scan_kernel<4, 1>, gla_scan_kernel<8, 1>, gla_scan_kernel<16, 1>, gla_scan_kernel<32, 1>, seen1, ggrid))) return e;
+        gla_seg_prefix_kernel<<<dim3(rb.E, a.H, 8), 256, 0, st>>>(rb, a);
+        if ((e = last_err())) return e;
+        e = scan(gla_scan_kernel<4, 2>, gla_scan_kernel<8, 2>, gla_scan_kernel<16, 2>, gla_scan_kernel<32, 2>, seen2, ggrid);
+    }
     if (e) return e;
     gla_out_kernel<<<dim3(rb.T, (a.H + 3) / 4), 128, 0, st>>>(a, rb.T);
     return last_err();

@@ -362,6 +362,26 @@ def test_long_context_decode():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("precision,tol", [("f32", F32_TOL), ("split", SPLIT_TOL)])
+def test_long_portions_scan_in_segments(precision, tol):
+    # from 512 rows on a portion's recurrence runs as four segments side by side; here on a carried state, beside a short request,
+    # with lengths that leave the last segment ragged and one key width that is not a multiple of four
+    cfg = config([layer(gla(heads=2, dim=32, vdim=40, tau=50.0, decay_rank=8), None), layer(gla(heads=3, dim=18, vdim=20, tau=20.0, decay_rank=4), moe(ff=24, experts=4, top=1, shared=0))],
+                 width=96, vocab=150, groups=2, taps=4)
+    m, w = make(cfg, 27, precision=precision, max_tokens=2048)
+    ids, other = tokens(1400, cfg["vocab"], 28), tokens(40, cfg["vocab"], 29)
+    want, want2 = oracle_logits(cfg, w, ids), oracle_logits(cfg, w, other)
+    s1 = m.seq_create()
+    a = m.step_batch([(0, ids[:100], [99])])
+    b = m.step_batch([(s1, other[:30], [29]), (0, ids[100:803], [0, 350, 702])])
+    c = m.step_batch([(0, ids[803:1399], [0, 595]), (s1, other[30:], [9])])
+    d = m.step_batch([(0, ids[1399:], [0])])
+    assert rel(np.concatenate([a, b[1:], c[:2], d]), want[[99, 100, 450, 802, 803, 1398, 1399]]) < tol
+    assert rel(np.stack([b[0], c[2]]), want2[[29, 39]]) < tol
+    m.close()
+
+
+@pytest.mark.gpu
 def test_greedy_generation_through_generate_and_the_scheduler():
     from crane_b200.scheduler import BatchScheduler
     m, w = make(FULL, 19, precision="f32", max_tokens=512)
