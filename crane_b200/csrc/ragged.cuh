@@ -166,7 +166,9 @@ struct CausalConvArgs {
 int causal_conv_launch(cudaStream_t st, const RaggedBatch& rb, const CausalConvArgs& a);
 int causal_conv_launch_count(const CausalConvArgs& a);
 
-// Every entry one row: out_h = rms_in_groups(x) * norm_w, out_u = out_h + conv(out_h) over the carried window, window moved on -- one launch
+// Every entry one row: out_h = rms_in_groups(x) * norm_w, out_u = out_h + conv(out_h) over the carried window, window moved on -- one launch,
+// for the sizes norm_conv_step_fits() accepts (the others take rms_rows + causal_conv)
+bool norm_conv_step_fits(int W, int groups, int taps);
 int norm_conv_step_launch(cudaStream_t st, const RaggedBatch& rb, const float* x, int ldx, int W, int groups, float eps, const float* norm_w,
                           int taps, const float* conv_w, float* state, const ActOut& out_h, const ActOut& out_u);
 

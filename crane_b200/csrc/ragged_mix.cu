@@ -137,75 +137,110 @@ __global__ void __launch_bounds__(128) headwise_linear_kernel(ActOut in, const b
     }
 }
 
-// Up to HWF_ROWS rows (a decode step): block = (64 output columns, head); its four warps split the head's n_in input rows between them,
-// a lane owns two neighbouring columns (one 4-byte load of the bf16 weights per input row, the warp reads 128 contiguous bytes), and
-// the warps' partial sums meet in warp order.
-constexpr int HWF_ROWS = 4;
-__global__ void __launch_bounds__(128) headwise_few_kernel(ActOut in, const bf16* __restrict__ w, int T, int n_in, int n_out, ActOut out) {
-    extern __shared__ float hwf_s[];                      // [T][n_in] inputs, then [4 warps][HWF_ROWS][64] partial sums
+// Up to HWF_ROWS rows (a decode step): block = (128 output columns, head); its sixteen warps split the head's n_in input rows between
+// them, a lane owns four neighbouring columns (one 8-byte load of the bf16 weights per input row, the warp reads 256 contiguous bytes;
+// a warp's handful of rows are all requested before the first is used), and the warps' partial sums meet in warp order.
+constexpr int HWF_ROWS = 4, HWF_WARPS = 16, HWF_COLS = 128;
+__global__ void __launch_bounds__(HWF_WARPS * 32) headwise_few_kernel(ActOut in, const bf16* __restrict__ w, int T, int n_in, int n_out, ActOut out) {
+    extern __shared__ float hwf_s[];                      // [T][n_in] inputs, then [warps][HWF_ROWS][HWF_COLS] partial sums
     float* xin = hwf_s;
-    float* part = hwf_s + (size_t)T * n_in;
-    const int h = blockIdx.y, c0 = blockIdx.x * 64, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* part = hwf_s + (((size_t)T * n_in + 3) & ~(size_t)3);
+    const int h = blockIdx.y, c0 = blockIdx.x * HWF_COLS, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < T * n_in; i += blockDim.x) { const int rr = i / n_in, j = i - rr * n_in; xin[i] = act_load(in, rr, h * n_in + j); }
     __syncthreads();
-    const int col = c0 + 2 * lane, per = (n_in + 3) / 4, j0 = warp * per, j1 = min(n_in, j0 + per);
-    const bool two = col + 1 < n_out && (n_out & 1) == 0;  // (an even width keeps every pair 4-byte aligned)
-    float acc[HWF_ROWS][2] = {};
-    if (col < n_out) {
-        const bf16* wh = w + (size_t)h * n_in * n_out + col;
-#pragma unroll 4
-        for (int j = j0; j < j1; ++j) {
-            float w0, w1 = 0.f;
-            if (two) { const uint32_t u = *reinterpret_cast<const uint32_t*>(wh + (size_t)j * n_out); w0 = bf16lo(u); w1 = bf16hi(u); }
-            else { w0 = __bfloat162float(wh[(size_t)j * n_out]); if (col + 1 < n_out) w1 = __bfloat162float(wh[(size_t)j * n_out + 1]); }
+    const int col = c0 + 4 * lane, per = (n_in + HWF_WARPS - 1) / HWF_WARPS, j0 = warp * per, j1 = min(n_in, j0 + per);
+    const bool vec = (n_out & 3) == 0;                     // (then every group of four starts on an 8-byte boundary)
+    float acc[HWF_ROWS][4] = {};
+    const bf16* wh = w + (size_t)h * n_in * n_out + col;
+    for (int jb = j0; jb < j1; jb += 8) {
+        float wv[8][4];
 #pragma unroll
-            for (int rr = 0; rr < HWF_ROWS; ++rr) if (rr < T) { const float xv = xin[rr * n_in + j]; acc[rr][0] = fmaf(xv, w0, acc[rr][0]); acc[rr][1] = fmaf(xv, w1, acc[rr][1]); }
+        for (int u = 0; u < 8; ++u) {
+            const int j = jb + u;
+            wv[u][0] = wv[u][1] = wv[u][2] = wv[u][3] = 0.f;
+            if (j < j1 && col < n_out) {
+                if (vec) { const uint2 t = *reinterpret_cast<const uint2*>(wh + (size_t)j * n_out); wv[u][0] = bf16lo(t.x); wv[u][1] = bf16hi(t.x); wv[u][2] = bf16lo(t.y); wv[u][3] = bf16hi(t.y); }
+                else for (int c = 0; c < 4; ++c) if (col + c < n_out) wv[u][c] = __bfloat162float(wh[(size_t)j * n_out + c]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = jb + u;
+            if (j >= j1) break;
+#pragma unroll
+            for (int rr = 0; rr < HWF_ROWS; ++rr)
+                if (rr < T) {
+                    const float xv = xin[rr * n_in + j];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[rr][c] = fmaf(xv, wv[u][c], acc[rr][c]);
+                }
         }
     }
 #pragma unroll
-    for (int rr = 0; rr < HWF_ROWS; ++rr) { part[(warp * HWF_ROWS + rr) * 64 + 2 * lane] = acc[rr][0]; part[(warp * HWF_ROWS + rr) * 64 + 2 * lane + 1] = acc[rr][1]; }
+    for (int rr = 0; rr < HWF_ROWS; ++rr)
+        *reinterpret_cast<float4*>(part + ((size_t)warp * HWF_ROWS + rr) * HWF_COLS + 4 * lane) = make_float4(acc[rr][0], acc[rr][1], acc[rr][2], acc[rr][3]);
     __syncthreads();
-    for (int i = threadIdx.x; i < T * 64; i += blockDim.x) {
-        const int rr = i >> 6, c = i & 63;
-        if (c0 + c < n_out) store_act(out, rr, h * n_out + c0 + c, ((part[rr * 64 + c] + part[(HWF_ROWS + rr) * 64 + c]) + part[(2 * HWF_ROWS + rr) * 64 + c]) + part[(3 * HWF_ROWS + rr) * 64 + c]);
+    for (int i = threadIdx.x; i < T * HWF_COLS; i += blockDim.x) {
+        const int rr = i / HWF_COLS, c = i - rr * HWF_COLS;
+        if (c0 + c >= n_out) continue;
+        float sum = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < HWF_WARPS; ++wq) sum += part[((size_t)wq * HWF_ROWS + rr) * HWF_COLS + c];
+        store_act(out, rr, h * n_out + c0 + c, sum);
     }
 }
 
 // Every entry one token: the sublayer's norm (RMS in equal groups), the convolution over the carried window and the window's shift
-// in one pass.  Block per entry; h = norm output goes to out_h, h + conv(h) to out_u.
-__global__ void __launch_bounds__(256) norm_conv_step_kernel(RaggedBatch rb, const float* __restrict__ x, int ldx, int W, int groups, float eps,
-                                                             const float* __restrict__ nw, int taps, const float* __restrict__ cw, float* state,
-                                                             ActOut out_h, ActOut out_u) {
-    __shared__ float red[8];
-    const int e = blockIdx.x, r = rb.ent_row0[e], slot = rb.ent_slot[e], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// in one pass.  Block per entry, NCS columns per thread; everything the row needs (its x, the norm and tap weights, the window) is
+// requested up front, so the kernel costs one trip to memory.  h = norm output goes to out_h, h + conv(h) to out_u.
+constexpr int NCS_COLS = 4, NCS_GROUPS = 8;
+template <int TAPS>
+__global__ void __launch_bounds__(1024) norm_conv_step_kernel(RaggedBatch rb, const float* __restrict__ x, int ldx, int W, int groups, float eps,
+                                                              const float* __restrict__ nw, const float* __restrict__ cw, float* state,
+                                                              ActOut out_h, ActOut out_u) {
+    __shared__ float red[NCS_GROUPS][32];
+    const int e = blockIdx.x, r = rb.ent_row0[e], slot = rb.ent_slot[e], lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const float* xr = x + (size_t)r * ldx;
-    float* win = state + (size_t)slot * (taps - 1) * W;
+    float* win = state + (size_t)slot * (TAPS - 1) * W;
     const int part = W / groups;
-    for (int g = 0; g < groups; ++g) {
-        const int c0 = g * part;
-        float ss = 0.f;
-        for (int c = threadIdx.x; c < part; c += 256) ss = fmaf(xr[c0 + c], xr[c0 + c], ss);
-        ss = warp_sum(ss);
-        if (g) __syncthreads();
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
+    float xv[NCS_COLS], wn[NCS_COLS], tw[NCS_COLS][TAPS], old[NCS_COLS][TAPS > 1 ? TAPS - 1 : 1];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) tot += red[k];
-        const float inv = 1.f / sqrtf(tot / (float)part + eps);
-        for (int c = c0 + threadIdx.x; c < c0 + part; c += 256) {
-            const float u = xr[c] * inv * nw[c];
-            float acc = 0.f;
-            for (int k = 0; k < taps - 1; ++k) {
-                const float wv = win[(size_t)k * W + c];
-                acc = fmaf(cw[(size_t)c * taps + k], wv, acc);
-                if (k > 0) win[(size_t)(k - 1) * W + c] = wv;
-            }
-            acc = fmaf(cw[(size_t)c * taps + taps - 1], u, acc);
-            if (taps > 1) win[(size_t)(taps - 2) * W + c] = u;
-            store_act(out_h, r, c, u);
-            store_act(out_u, r, c, u + acc);
+    for (int k = 0; k < NCS_COLS; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        const bool in = c < W;
+        xv[k] = in ? xr[c] : 0.f;
+        wn[k] = in ? nw[c] : 0.f;
+#pragma unroll
+        for (int t = 0; t < TAPS; ++t) tw[k][t] = in ? cw[(size_t)c * TAPS + t] : 0.f;
+#pragma unroll
+        for (int t = 0; t < TAPS - 1; ++t) old[k][t] = in ? win[(size_t)t * W + c] : 0.f;
+    }
+    for (int g = 0; g < groups; ++g) {                      // a group's sum of squares: a thread's own columns in order, the warp's tree, the warps in order
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < NCS_COLS; ++k) { const int c = threadIdx.x + k * blockDim.x; if (c < W && c / part == g) ss = fmaf(xv[k], xv[k], ss); }
+        ss = warp_sum(ss);
+        if (lane == 0) red[g][warp] = ss;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < NCS_COLS; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c >= W) continue;
+        const int g = c / part;
+        float tot = 0.f;
+        for (int wq = 0; wq < nwarp; ++wq) tot += red[g][wq];
+        const float u = xv[k] * (1.f / sqrtf(tot / (float)part + eps)) * wn[k];
+        float acc = 0.f;
+#pragma unroll
+        for (int t = 0; t < TAPS - 1; ++t) {
+            acc = fmaf(tw[k][t], old[k][t], acc);
+            if (t > 0) win[(size_t)(t - 1) * W + c] = old[k][t];
         }
+        acc = fmaf(tw[k][TAPS - 1], u, acc);
+        if (TAPS > 1) win[(size_t)(TAPS - 2) * W + c] = u;
+        store_act(out_h, r, c, u);
+        store_act(out_u, r, c, u + acc);
     }
 }
 
@@ -418,10 +453,17 @@ int causal_conv_launch(cudaStream_t st, const RaggedBatch& rb, const CausalConvA
     if (a.taps > 1) causal_conv_window_kernel<<<dim3((a.C + 127) / 128, rb.E), 128, 0, st>>>(rb, a);
     return last_err();
 }
+bool norm_conv_step_fits(int W, int groups, int taps) { return groups >= 1 && groups <= NCS_GROUPS && W % groups == 0 && taps >= 1 && taps <= 4 && W <= 1024 * NCS_COLS; }
 int norm_conv_step_launch(cudaStream_t st, const RaggedBatch& rb, const float* x, int ldx, int W, int groups, float eps, const float* norm_w,
                           int taps, const float* conv_w, float* state, const ActOut& out_h, const ActOut& out_u) {
-    if (groups < 1 || W % groups || taps < 1) return -1000;
-    norm_conv_step_kernel<<<rb.E, 256, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, taps, conv_w, state, out_h, out_u);
+    if (!norm_conv_step_fits(W, groups, taps)) return -1000;
+    const int threads = std::min(1024, std::max(128, ((W + NCS_COLS - 1) / NCS_COLS + 31) / 32 * 32));
+    switch (taps) {
+        case 1: norm_conv_step_kernel<1><<<rb.E, threads, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, conv_w, state, out_h, out_u); break;
+        case 2: norm_conv_step_kernel<2><<<rb.E, threads, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, conv_w, state, out_h, out_u); break;
+        case 3: norm_conv_step_kernel<3><<<rb.E, threads, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, conv_w, state, out_h, out_u); break;
+        default: norm_conv_step_kernel<4><<<rb.E, threads, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, conv_w, state, out_h, out_u); break;
+    }
     return last_err();
 }
 int gated_add_launch(cudaStream_t st, float* x, int ldx, const float* y, int ldy, const float* gate, int ldg, const float* bias, int T, int W) {
@@ -442,10 +484,10 @@ int headwise_linear_launch(cudaStream_t st, const ActOut& in, const bf16* w, int
     const size_t smem = (size_t)HW_ROWS * n_in * sizeof(float);
     if ((!in.f && !in.hi) || smem > 200 * 1024) return -1000;
     if (T <= HWF_ROWS) {
-        const size_t sf = ((size_t)T * n_in + 4 * HWF_ROWS * 64) * sizeof(float);
+        const size_t sf = ((size_t)((T * n_in + 3) & ~3) + (size_t)HWF_WARPS * HWF_ROWS * HWF_COLS) * sizeof(float);
         static SmemOptIn seen_few;
         if (const int e = ensure_dyn_smem(headwise_few_kernel, sf, seen_few)) return e;
-        headwise_few_kernel<<<dim3((n_out + 63) / 64, H), 128, sf, st>>>(in, w, T, n_in, n_out, out);
+        headwise_few_kernel<<<dim3((n_out + HWF_COLS - 1) / HWF_COLS, H), HWF_WARPS * 32, sf, st>>>(in, w, T, n_in, n_out, out);
         return last_err();
     }
     static SmemOptIn seen;
