@@ -1853,6 +1853,7 @@ int crane_b200_create(const char* config_json, int device_ordinal, crane_b200_mo
         if (device_ordinal < 0 || device_ordinal >= ndev) fail(CRANE_B200_INVALID_ARG, "device ordinal %d of %d", device_ordinal, ndev);
         m->device = device_ordinal;
         CUDA_OK(cudaSetDevice(device_ordinal));
+        cudaGetLastError();      // a new handle starts from a clean slate: an error that another handle left unread is not this one's
         cudaDeviceProp prop;
         CUDA_OK(cudaGetDeviceProperties(&prop, device_ordinal));
         if (prop.major != 10) fail(CRANE_B200_UNSUPPORTED, "device %s is sm_%d%d; this library is built for sm_100a only", prop.name, prop.major, prop.minor);

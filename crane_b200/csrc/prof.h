@@ -87,7 +87,7 @@ class PassProfiler {
         }
         for (int i = 0; i + 1 < n_ev; ++i) {
             float ms = 0.f;
-            if (cudaEventElapsedTime(&ms, ev[i], ev[i + 1]) != cudaSuccess) continue;
+            if (cudaEventElapsedTime(&ms, ev[i], ev[i + 1]) != cudaSuccess) { cudaGetLastError(); continue; }      // (the refusal must not surface at a later launch)
             window[kind].dev_ms[span_of[i]] += ms; total[kind].dev_ms[span_of[i]] += ms;
             window[kind].device_ms += ms; total[kind].device_ms += ms;
         }

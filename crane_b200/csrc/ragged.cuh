@@ -7,7 +7,10 @@
 //   (any key width, any value width, grouped queries, keys / values optionally owned by another layer), the Mamba-2 mixer
 //   (causal depthwise convolution with carried window, selective state-space scan with carried f32 state, gated grouped RMS
 //   norm), a clamped gated feed-forward, and a mixture of experts (softmax or sigmoid scores, a selection bias, group-limited
-//   choice, plain or gated experts; router, counting sort, grouped linears, ordered combine with a per-column scale).  See ragged.cu.
+//   choice, plain or gated experts, SiLU or clamped units, the score on the expert's input or output; router, counting sort, grouped
+//   linears, ordered combine with a per-column scale, an every-token expert and a sigmoid gate).  See ragged.cu.  Further, in
+//   ragged_mix.cu: a carried causal convolution in front of a sublayer, latent attention (one normalised low-rank row cached per
+//   token), block-diagonal per-head linears, gated linear attention with a decay per key channel, a soft cap on logits.
 #pragma once
 
 #include "common.cuh"

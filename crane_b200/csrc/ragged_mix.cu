@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(1024) norm_conv_step_kernel(RaggedBatch rb, co
 // decay[r, c] = sigmoid(z)^(1 / tau) = exp(log_sigmoid(z) / tau), z = a2[c, :] . a[r, :] + b[c]; log_sigmoid(z) = min(z, 0) - log1p(e^-|z|)
 // (a2 is stored transposed, [rank, H * d]: neighbouring threads read neighbouring channels; GLA_DROWS rows share each weight)
 constexpr int GLA_DROWS = 8;
-__global__ void __launch_bounds__(256) gla_decay_kernel(GlaArgs a, int T) {
+__global__ void __launch_bounds__(128) gla_decay_kernel(GlaArgs a, int T) {
     extern __shared__ float lowrank[];                    // [GLA_DROWS][rank]
     const int r0 = blockIdx.x * GLA_DROWS, C = a.H * a.d, nr = min(GLA_DROWS, T - r0);
     for (int i = threadIdx.x; i < GLA_DROWS * a.rank; i += blockDim.x) {
@@ -256,11 +256,12 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(GlaArgs a, int T) {
         lowrank[i] = rr < nr ? a.proj[(size_t)(r0 + rr) * a.ld + 2 * C + 2 * a.H * a.dv + j] : 0.f;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         float z[GLA_DROWS];
         const float b = a.a2_b[c];
 #pragma unroll
         for (int rr = 0; rr < GLA_DROWS; ++rr) z[rr] = b;
+#pragma unroll 8
         for (int j = 0; j < a.rank; ++j) {
             const float wv = a.a2[(size_t)j * C + c];
 #pragma unroll
@@ -500,7 +501,8 @@ size_t gla_seg_floats(int entries, int H, int d, int dv) { return (size_t)entrie
 size_t gla_seg_decay_offset(int entries, int H, int d, int dv) { return (size_t)entries * GLA_SEGS * H * (size_t)d * dv; }
 int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a) {
     if (a.d < 1 || a.d > 256 || a.dv < 1 || a.rank < 1 || a.rank > 8192) return -1000;
-    gla_decay_kernel<<<(rb.T + GLA_DROWS - 1) / GLA_DROWS, 256, (size_t)GLA_DROWS * a.rank * sizeof(float), st>>>(a, rb.T);
+    const int row_blocks = (rb.T + GLA_DROWS - 1) / GLA_DROWS;      // few rows: the channels spread over blocks as well
+    gla_decay_kernel<<<dim3(row_blocks, row_blocks >= 64 ? 1 : std::max(1, std::min(16, (a.H * a.d + 127) / 128))), 128, (size_t)GLA_DROWS * a.rank * sizeof(float), st>>>(a, rb.T);
     int e = last_err();
     if (e) return e;
     const int nr = (a.d + GLA_NS - 1) / GLA_NS, R = nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
