@@ -441,8 +441,8 @@ def gavipel_tensor_specs(cfg: dict):
 
 
 def nifarax_config(width=1024, vocab=65536, layers=12, gla_every=3, heads=8, dim=128, vdim=128, q_rank=512, kv_rank=256, gla_heads=8,
-                   gla_dim=64, gla_vdim=128, tau=16.0, decay_rank=32, experts=8, top=4, expert_ff=896, shared_ff=896, limit=7.0, taps=4,
-                   norm_groups=2, share_last_gla=True):
+                   gla_dim=64, gla_vdim=128, tau=12.0, decay_rank=32, experts=8, top=4, expert_ff=896, shared_ff=896, limit=7.0, taps=4,
+                   norm_groups=4, share_last_gla=True):
     """`layers` layers, every `gla_every`-th one gated linear attention and the others latent attention, each with a mixture of clamped
     gated experts and a shared expert; the last gla layer reuses the first one's tensors.  `decay_rank` is not read by the engine (the
     rank comes with the tensors); it tells `nifarax_tensor_specs` which shape to make."""
@@ -461,8 +461,8 @@ def nifarax_config(width=1024, vocab=65536, layers=12, gla_every=3, heads=8, dim
     glas = [i for i, L in enumerate(ls) if L["type"] == "gla"]
     if share_last_gla and len(glas) > 1:
         ls[glas[-1]]["weights_of"] = glas[0]
-    return {"architecture": "Nifarax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": norm_groups}, "canon": {"taps": taps},
-            "logit_softcap": 30.0, "layers": ls}
+    return {"architecture": "Nifarax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": norm_groups}, "canon": {"taps": taps},
+            "logit_softcap": 50.0, "layers": ls}
 
 
 def nifarax_tensor_specs(cfg: dict):

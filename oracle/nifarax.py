@@ -125,8 +125,9 @@ def softcap(z, cap):
 # ---------------------------------------------------------------------------------------------- the model
 def weight_layer(config, i):
     """The layer whose tensors layer i reads."""
-    j = config["layers"][i].get("weights_of")
-    return i if j is None else int(j)
+    while config["layers"][i].get("weights_of") is not None:
+        i = int(config["layers"][i]["weights_of"])
+    return i
 
 
 class State:

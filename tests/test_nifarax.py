@@ -63,6 +63,7 @@ SINGLE = {
     "experts_all_chosen": config([layer(gla(), moe(ff=28, experts=4, top=4, shared=16))]),
     "experts_shared": config([layer(latent(), moe())]),
     "shared_weights": config([layer(gla()), layer(latent()), layer(gla(), weights_of=0), layer(latent(), weights_of=1)]),
+    "shared_weights_from_a_later_layer_and_through_another": config([layer(latent(), weights_of=2), layer(latent(), weights_of=0), layer(latent())]),
     "no_cap_needed": config([layer(latent()), layer(gla())], cap=500.0),
 }
 
@@ -420,9 +421,12 @@ def test_greedy_generation_through_generate_and_the_scheduler():
 
 
 @pytest.mark.gpu
-def test_wide_latents_and_many_rows_take_the_tensor_core_paths():
-    # a 128-wide latent through the flash kernel, enough (row, expert) pairs for the per-expert GEMMs
-    cfg = config([layer(latent(heads=4, dim=64, vdim=64, q_rank=96, kv_rank=128, scale=0.12), moe(ff=64, experts=4, top=2, shared=96)),
+@pytest.mark.parametrize("att", [latent(heads=4, dim=64, vdim=64, q_rank=96, kv_rank=128, scale=0.12), latent(heads=3, dim=128, vdim=128, q_rank=40, kv_rank=256, scale=0.09),
+                                 latent(heads=2, dim=64, vdim=32, q_rank=64, kv_rank=64, scale=0.12)])
+def test_wide_latents_and_many_rows_take_the_tensor_core_paths(att):
+    # a 64-, 128- or 256-wide latent through the flash kernel (whole prompts with equal key and value widths: keys and values built
+    # outright), enough (row, expert) pairs for the per-expert GEMMs
+    cfg = config([layer(att, moe(ff=64, experts=4, top=2, shared=96)),
                   layer(gla(heads=2, dim=64, vdim=128, tau=12.0, decay_rank=16), moe(ff=64, experts=4, top=2, shared=0))], width=256, vocab=300, groups=2, taps=4)
     m, w = make(cfg, 21, precision="split")
     ids = tokens(400, cfg["vocab"], 22)
