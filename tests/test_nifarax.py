@@ -62,6 +62,8 @@ SINGLE = {
     "experts_top1_no_shared": config([layer(latent(), moe(ff=30, experts=5, top=1, shared=0))]),
     "experts_all_chosen": config([layer(gla(), moe(ff=28, experts=4, top=4, shared=16))]),
     "experts_shared": config([layer(latent(), moe())]),
+    "one_expert_one_head": config([layer(latent(heads=1, dim=16, vdim=12, q_rank=8, kv_rank=20), moe(ff=16, experts=1, top=1, shared=0)),
+                                   layer(gla(heads=1, dim=8, vdim=8, tau=2.0, decay_rank=1), moe(ff=8, experts=1, top=1, shared=8))], width=64, vocab=70, groups=1, taps=2),
     "shared_weights": config([layer(gla()), layer(latent()), layer(gla(), weights_of=0), layer(latent(), weights_of=1)]),
     "shared_weights_from_a_later_layer_and_through_another": config([layer(latent(), weights_of=2), layer(latent(), weights_of=0), layer(latent())]),
     "no_cap_needed": config([layer(latent()), layer(gla())], cap=500.0),
