@@ -175,9 +175,6 @@ bool norm_conv_step_fits(int W, int groups, int taps);
 int norm_conv_step_launch(cudaStream_t st, const RaggedBatch& rb, const float* x, int ldx, int W, int groups, float eps, const float* norm_w,
                           int taps, const float* conv_w, float* state, const ActOut& out_h, const ActOut& out_u);
 
-// x[r, c] += sigmoid(gate[r, c] + bias[c]) * y[r, c]
-int gated_add_launch(cudaStream_t st, float* x, int ldx, const float* y, int ldy, const float* gate, int ldg, const float* bias, int T, int W);
-
 // Latent attention, first half: proj [T, ld] holds the query latent (q_rank columns) and the key / value latent (kv_rank columns).
 // Each is RMS-normed with its weight; the query latent goes to cq, the key / value latent to the sequence's page at the row's position
 // (one "head" of width kv_rank: the pool serves as keys and as values).

@@ -1,5 +1,5 @@
 // Ragged-batch kernels of layers that run their sublayers one after the other (see ragged.cuh): a carried causal convolution in
-// front of a sublayer, a sigmoid gate on its way back into the residual, latent attention (only a normalised low-rank row is kept
+// front of a sublayer, latent attention (only a normalised low-rank row is kept
 // per token; the per-head key and value maps are applied to the query and to the attention's output instead), gated linear
 // attention with a decay per key channel, and a soft cap on the logits.  All of it is f32 arithmetic on CUDA cores; a row's result
 // depends on its own sequence only (every sum runs in an order fixed by the row's position and the launch constants).
@@ -57,14 +57,6 @@ __global__ void causal_conv_step_kernel(RaggedBatch rb, CausalConvArgs a) {
     acc = fmaf(a.w[(size_t)c * taps + taps - 1], u, acc);
     if (taps > 1) win[(size_t)(taps - 2) * a.C + c] = u;
     store_act(a.out, r, c, a.add_input ? u + acc : acc);
-}
-
-__global__ void gated_add_kernel(float* __restrict__ x, int ldx, const float* __restrict__ y, int ldy, const float* __restrict__ gate, int ldg,
-                                 const float* __restrict__ bias, int W) {
-    const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= W) return;
-    const float g = gate[(size_t)r * ldg + c] + (bias ? bias[c] : 0.f);
-    x[(size_t)r * ldx + c] += y[(size_t)r * ldy + c] / (1.f + expf(-g));
 }
 
 __global__ void softcap_rows_kernel(const float* __restrict__ src, int lds, int V, float cap, float* __restrict__ dst, int ldd) {
@@ -465,10 +457,6 @@ int norm_conv_step_launch(cudaStream_t st, const RaggedBatch& rb, const float* x
         case 3: norm_conv_step_kernel<3><<<rb.E, threads, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, conv_w, state, out_h, out_u); break;
         default: norm_conv_step_kernel<4><<<rb.E, threads, 0, st>>>(rb, x, ldx, W, groups, eps, norm_w, conv_w, state, out_h, out_u); break;
     }
-    return last_err();
-}
-int gated_add_launch(cudaStream_t st, float* x, int ldx, const float* y, int ldy, const float* gate, int ldg, const float* bias, int T, int W) {
-    gated_add_kernel<<<dim3((W + 127) / 128, T), 128, 0, st>>>(x, ldx, y, ldy, gate, ldg, bias, W);
     return last_err();
 }
 int softcap_rows_launch(cudaStream_t st, const float* src, int lds, int R, int V, float cap, float* dst, int ldd) {
