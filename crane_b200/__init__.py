@@ -644,6 +644,15 @@ class NifaraxModel(FosovikModel):
     tanh soft cap.  Same entry points and engine options as `FosovikModel`."""
 
 
+class PuzonexModel(FosovikModel):
+    """A layer-list decoder ("architecture": "Puzonex"): the stream starts as the embedding row plus a sinusoidal position vector; each
+    layer runs a mixer and then a tanh-GELU gated feed-forward, both reading the stream itself, with the RMS norm on each sublayer's
+    way back.  Mixers: grouped-query attention with projection biases, capped scores, a logarithmic distance penalty, a sliding window
+    and a learned sink; Mamba-1 (selective scan with an f32 state per channel); or windowed attention with a bucketed distance table
+    and an output gate side by side with a matrix memory under exponential gates (mLSTM), their normalised outputs averaged.  Same
+    entry points and engine options as `FosovikModel`."""
+
+
 # config.json -> model class, as `model_factory::create_backend` picks a backend by architecture (crane-serve/src/engine/model_factory.rs:471-560)
 def model_class(config: dict):
     if config.get("architecture") == "Fosovik":
@@ -652,6 +661,8 @@ def model_class(config: dict):
         return GavipelModel
     if config.get("architecture") == "Nifarax":
         return NifaraxModel
+    if config.get("architecture") == "Puzonex":
+        return PuzonexModel
     if "talker_config" in config:
         return Qwen3TTSModel
     if "vision_config" in config:

@@ -107,20 +107,22 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 // ---- math ----------------------------------------------------------------------------
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
-// gated unit of a (gate, up) pair: SiLU(g) * u, or with a limit L > 0 the clamped form min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1)
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+// gated unit of a (gate, up) pair: limit == 0: SiLU(g) * u;  limit > 0: the clamped form min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1);
+// limit < 0: gelu_tanh(g) * u
 __device__ __forceinline__ float glu_pair_f(float g, float u, float limit) {
     if (limit > 0.f) {
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
         return g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
     }
+    if (limit < 0.f) return gelu_tanh_f(g) * u;
     return silu_f(g) * u;
 }
 __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f)); }
-__device__ __forceinline__ float gelu_tanh_f(float x) {
-    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-    return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
-}
 
 
 // Host: cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is per DEVICE -- one process may drive a handle on every GPU of the box --

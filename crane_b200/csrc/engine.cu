@@ -190,7 +190,7 @@ struct FosovikModel;   // layer-list models (engine_fosovik.inc)
 struct crane_b200_model {
     // ---- configuration ----
     int device = 0, num_sms = 148;
-    FosovikModel* fsv = nullptr;            // "architecture": "Fosovik" or "Gavipel" -- the handle then runs ragged-batch steps (engine_fosovik.inc)
+    FosovikModel* fsv = nullptr;            // "architecture": "Fosovik", "Gavipel", "Nifarax" or "Puzonex" -- the handle then runs ragged-batch steps (engine_fosovik.inc)
     bool is_vl = false;
     int V = 0, H = 0, I = 0, L = 0, nh = 0, nkv = 0, D = 0;
     float eps = 1e-6f;
@@ -1860,7 +1860,7 @@ int crane_b200_create(const char* config_json, int device_ordinal, crane_b200_mo
         m->num_sms = prop.multiProcessorCount;
         {
             cbjson::Value root = cbjson::Parser(config_json).parse();
-            if (root.type == cbjson::Value::OBJ && (root.string("architecture", "") == "Fosovik" || root.string("architecture", "") == "Gavipel" || root.string("architecture", "") == "Nifarax")) {
+            if (root.type == cbjson::Value::OBJ && (root.string("architecture", "") == "Fosovik" || root.string("architecture", "") == "Gavipel" || root.string("architecture", "") == "Nifarax" || root.string("architecture", "") == "Puzonex")) {
                 m->fsv = new FosovikModel();
                 m->fsv->device = device_ordinal; m->fsv->num_sms = m->num_sms;
                 m->fsv->parse(root);

@@ -22,6 +22,59 @@ __global__ void embed_scale_rows_kernel(const int* __restrict__ ids, int T, cons
     for (int c = threadIdx.x; c < W; c += blockDim.x) x[(size_t)r * ldx + c] = __bfloat162float(e[c]) * scale;
 }
 
+__global__ void embed_sinpos_rows_kernel(const int* __restrict__ ids, const int* __restrict__ row_pos, const bf16* __restrict__ embed, int W,
+                                         const float* __restrict__ freq, float* __restrict__ x, int ldx) {
+    const int r = blockIdx.x;
+    const bf16* e = embed + (size_t)ids[r] * W;
+    const float pos = (float)row_pos[r];
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float ang = pos * freq[c >> 1];
+        x[(size_t)r * ldx + c] = __bfloat162float(e[c]) + ((c & 1) ? cosf(ang) : sinf(ang));
+    }
+}
+
+// Block per row.  One input: x += rms(y1 + b1) * norm_w.  Two inputs: v = (rms(y1 + b1) * w1 + rms(y2) * w2) / 2, x += rms(v) * norm_w.
+__global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restrict__ y1, int ld1, const float* __restrict__ b1, const float* __restrict__ w1,
+                                                            const float* __restrict__ y2, int ld2, const float* __restrict__ w2,
+                                                            const float* __restrict__ norm_w, float eps, float* __restrict__ x, int ldx, int W) {
+    __shared__ float red[3][8];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* a = y1 + (size_t)r * ld1;
+    const float* b = y2 ? y2 + (size_t)r * ld2 : nullptr;
+    float* xr = x + (size_t)r * ldx;
+    auto total = [&](float v, int k) {      // fixed order: thread-strided partial sums, warp tree, warps in order
+        v = warp_sum(v);
+        if (lane == 0) red[k][warp] = v;
+        __syncthreads();
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[k][w];
+        return t;
+    };
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < W; c += 256) {
+        const float u = a[c] + (b1 ? b1[c] : 0.f);
+        sa = fmaf(u, u, sa);
+        if (b) sb = fmaf(b[c], b[c], sb);
+    }
+    const float ia = 1.f / sqrtf(total(sa, 0) / (float)W + eps);
+    if (!b) {
+        for (int c = threadIdx.x; c < W; c += 256) xr[c] += (a[c] + (b1 ? b1[c] : 0.f)) * ia * norm_w[c];
+        return;
+    }
+    const float ib = 1.f / sqrtf(total(sb, 1) / (float)W + eps);
+    float sv = 0.f;
+    for (int c = threadIdx.x; c < W; c += 256) {
+        const float v = 0.5f * ((a[c] + (b1 ? b1[c] : 0.f)) * ia * (w1 ? w1[c] : 1.f) + b[c] * ib * (w2 ? w2[c] : 1.f));
+        sv = fmaf(v, v, sv);
+    }
+    const float iv = 1.f / sqrtf(total(sv, 2) / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += 256) {
+        const float v = 0.5f * ((a[c] + (b1 ? b1[c] : 0.f)) * ia * (w1 ? w1[c] : 1.f) + b[c] * ib * (w2 ? w2[c] : 1.f));
+        xr[c] += v * iv * norm_w[c];
+    }
+}
+
 __global__ void dyt_rows_kernel(const float* __restrict__ x, int ldx, const int* __restrict__ rows, int W, const float* __restrict__ alpha,
                                 const float* __restrict__ w, const float* __restrict__ b, ActOut out) {
     const int r = blockIdx.x, src = rows ? rows[r] : r;
@@ -118,10 +171,12 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
 template <typename KT>
 __global__ void attn_prep_kernel(RaggedBatch rb, AttnPrepArgs a) {
     extern __shared__ float rot_cs[];                    // [rot_dims / 2] cos, then sin
+    __shared__ float whole[2][8];
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int e = rb.row_entry[r], pos = rb.row_pos[r], slot = rb.ent_slot[e];
     const float* row = a.qkv + (size_t)r * a.ld;
-    const int nheads = a.H + (a.has_kv ? 2 * a.G : 0);
+    const int nk = a.has_kv ? a.G : 0, nv = (a.has_kv && !a.v_from_k) ? a.G : 0;
+    const int nheads = a.H + nk + nv;
     const int nrot = a.rot_dims / 2;
     if (nrot > 0) {
         for (int i = threadIdx.x; i < nrot; i += blockDim.x) {
@@ -131,23 +186,53 @@ __global__ void attn_prep_kernel(RaggedBatch rb, AttnPrepArgs a) {
         }
         __syncthreads();
     }
+    // one statistic over all query heads and one over all key heads: thread-strided partial sums, warp tree, warps in order
+    float inv_whole[2] = {1.f, 1.f};
+    if (a.whole_norm && !a.no_norm) {
+        for (int which = 0; which < 2; ++which) {
+            const int n = which ? nk * a.d : a.H * a.d, off = which ? a.H * a.d : 0;
+            float ss = 0.f;
+            for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = row[off + c] + (a.bias ? a.bias[off + c] : 0.f); ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            if (lane == 0) whole[which][warp] = ss;
+        }
+        __syncthreads();
+        for (int which = 0; which < 2; ++which) {
+            const int n = which ? nk * a.d : a.H * a.d;
+            float tot = 0.f;
+            for (int w = 0; w < nw; ++w) tot += whole[which][w];
+            inv_whole[which] = n > 0 ? 1.f / sqrtf(tot / (float)n + a.eps) : 1.f;
+        }
+    }
     float temp = 1.f;
     if (a.temp_every > 0) temp = 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
     const int page = a.has_kv ? a.block_table[(size_t)slot * a.max_pages + pos / KV_PAGE] : 0;
     for (int hh = warp; hh < nheads; hh += nw) {
-        if (hh < a.H + a.G) {            // q or k head: RMS norm over d
+        if (hh < a.H + nk) {             // q or k head: RMS norm over d (or the row's whole-projection statistic)
             const bool isq = hh < a.H;
             const float* src = row + (size_t)hh * a.d;
+            const float* bsrc = a.bias ? a.bias + (size_t)hh * a.d : nullptr;
             const float* nwt = isq ? a.q_norm_w : a.k_norm_w;
+            if (nwt && a.whole_norm) nwt += (size_t)(isq ? hh : hh - a.H) * a.d;
             float ss = 0.f;
-            for (int c = lane; c < a.d; c += 32) ss += src[c] * src[c];
+            for (int c = lane; c < a.d; c += 32) { const float v = src[c] + (bsrc ? bsrc[c] : 0.f); ss += v * v; }
             ss = warp_sum(ss);
-            const float inv = a.no_norm ? 1.f : 1.f / sqrtf(ss / (float)a.d + a.eps) * (isq ? temp : 1.f);
-            KT* dst = nullptr;
-            if (!isq) dst = (KT*)a.k_pool + (((size_t)page * a.G + (hh - a.H)) * KV_PAGE + (pos % KV_PAGE)) * a.d;
+            float inv = a.no_norm ? 1.f : (a.whole_norm ? inv_whole[isq ? 0 : 1] : 1.f / sqrtf(ss / (float)a.d + a.eps)) * (isq ? temp : 1.f);
+            if (isq && a.q_head_scale) inv *= a.q_head_scale[hh];
+            KT* dst = nullptr; KT* dstv = nullptr;
+            if (!isq) {
+                const size_t at = ((size_t)page * a.G + (hh - a.H)) * KV_PAGE + (pos % KV_PAGE);
+                dst = (KT*)a.k_pool + at * a.d;
+                if (a.v_from_k) dstv = (KT*)a.v_pool + at * a.dv;
+            }
             // a lane owns the pairs (2i, 2i + 1), i = lane, lane + 32, ...: both halves of a rotated pair are in one thread
             for (int c = 2 * lane; c < a.d; c += 64) {
-                float u = src[c] * inv, v = (c + 1 < a.d) ? src[c + 1] * inv : 0.f;
+                const float u0 = src[c] + (bsrc ? bsrc[c] : 0.f), v0 = (c + 1 < a.d) ? src[c + 1] + (bsrc ? bsrc[c + 1] : 0.f) : 0.f;
+                if (dstv) {               // the value is the key as projected
+                    kv_store<KT>(dstv + c, u0, a.kv_lo_off);
+                    if (c + 1 < a.d) kv_store<KT>(dstv + c + 1, v0, a.kv_lo_off);
+                }
+                float u = u0 * inv, v = v0 * inv;
                 if (nwt) { u *= nwt[c]; if (c + 1 < a.d) v *= nwt[c + 1]; }
                 if (c + 1 < a.rot_dims) {
                     const float cs = rot_cs[c >> 1], sn = rot_cs[nrot + (c >> 1)];
@@ -164,9 +249,17 @@ __global__ void attn_prep_kernel(RaggedBatch rb, AttnPrepArgs a) {
             }
         } else {
             const int g = hh - a.H - a.G;
-            const float* src = row + (size_t)(a.H + a.G) * a.d + (size_t)g * a.dv;
+            const size_t off = (size_t)(a.H + a.G) * a.d + (size_t)g * a.dv;
+            const float* src = row + off;
+            const float* bsrc = a.bias ? a.bias + off : nullptr;
             KT* dst = (KT*)a.v_pool + (((size_t)page * a.G + g) * KV_PAGE + (pos % KV_PAGE)) * a.dv;
-            for (int c = lane; c < a.dv; c += 32) kv_store<KT>(dst + c, src[c], a.kv_lo_off);
+            float inv = 1.f;
+            if (a.v_unit) {
+                float ss = 0.f;
+                for (int c = lane; c < a.dv; c += 32) { const float v = src[c] + (bsrc ? bsrc[c] : 0.f); ss += v * v; }
+                inv = 1.f / sqrtf(warp_sum(ss) / (float)a.dv + a.eps);
+            }
+            for (int c = lane; c < a.dv; c += 32) kv_store<KT>(dst + c, (src[c] + (bsrc ? bsrc[c] : 0.f)) * inv, a.kv_lo_off);
         }
     }
 }
@@ -295,6 +388,19 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
                     const float kf = kv_load<KT>(kr + c, a.kv_lo_off);
 #pragma unroll
                     for (int q = 0; q < REP; ++q) if (q < nh) sc[q] = fmaf(sq[q * d + c], kf, sc[q]);
+                }
+            }
+        }
+        if (seen && (a.softcap > 0.f || a.dist_r1 || a.dist_table)) {       // cap, then the distance terms (f32, the row's own distance to the key)
+            const int dist = pos - j;
+#pragma unroll
+            for (int q = 0; q < REP; ++q) {
+                if (q < nh) {
+                    float x = sc[q];
+                    if (a.softcap > 0.f) x = a.softcap * tanhf(x / a.softcap);
+                    if (a.dist_r1) x -= a.dist_r1[h0 + q] * log1pf(a.dist_r2[h0 + q] * (float)dist);
+                    if (a.dist_table) x += a.dist_table[(size_t)min(dist, a.dist_rows - 1) * a.H + h0 + q];
+                    sc[q] = x;
                 }
             }
         }
@@ -623,10 +729,10 @@ __global__ void clamped_glu_kernel(const float* __restrict__ gu, int ld, int str
     store_act(out, r, j, g / (1.f + __expf(-1.702f * g)) * (u + 1.f));
 }
 
-__global__ void silu_glu_kernel(const float* __restrict__ gu, int ld, int F, ActOut out) {
+__global__ void silu_glu_kernel(const float* __restrict__ gu, int ld, int F, ActOut out, float limit) {
     const int r = blockIdx.y, j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= F) return;
-    store_act(out, r, j, silu_f(gu[(size_t)r * ld + 2 * j]) * gu[(size_t)r * ld + 2 * j + 1]);
+    store_act(out, r, j, glu_pair_f(gu[(size_t)r * ld + 2 * j], gu[(size_t)r * ld + 2 * j + 1], limit < 0.f ? limit : 0.f));
 }
 
 // Router logits of one row by one warp: NB experts at a time share the loads of the f32 row; a lane owns 8 neighbouring columns per
@@ -971,6 +1077,16 @@ int embed_scale_rows_launch(cudaStream_t st, const int* ids, int T, const bf16* 
     embed_scale_rows_kernel<<<T, 128, 0, st>>>(ids, T, embed, W, scale, x, ldx);
     return last_err();
 }
+int embed_sinpos_rows_launch(cudaStream_t st, const int* ids, const int* row_pos, int T, const bf16* embed, int W, const float* freq, float* x, int ldx) {
+    embed_sinpos_rows_kernel<<<T, 128, 0, st>>>(ids, row_pos, embed, W, freq, x, ldx);
+    return last_err();
+}
+int post_norm_add_launch(cudaStream_t st, const float* y1, int ld1, const float* b1, const float* w1, const float* y2, int ld2, const float* w2,
+                         const float* norm_w, float eps, float* x, int ldx, int T, int W) {
+    if (!y1 || !norm_w) return -1000;
+    post_norm_add_kernel<<<T, 256, 0, st>>>(y1, ld1, b1, w1, y2, ld2, w2, norm_w, eps, x, ldx, W);
+    return last_err();
+}
 int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w, const float* b,
                     const ActOut& out) {
     dyt_rows_kernel<<<R, 128, 0, st>>>(x, ldx, rows, W, alpha, w, b, out);
@@ -1006,12 +1122,13 @@ int store_rows_launch(cudaStream_t st, const float* src, int lds, int T, int W, 
     store_rows_kernel<<<T, 128, 0, st>>>(src, lds, W, dst, col0);
     return last_err();
 }
-int silu_glu_launch(cudaStream_t st, const float* gu, int ld, int T, int F, const ActOut& out) {
-    silu_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, F, out);
+int silu_glu_launch(cudaStream_t st, const float* gu, int ld, int T, int F, const ActOut& out, float limit) {
+    silu_glu_kernel<<<dim3((F + 127) / 128, T), 128, 0, st>>>(gu, ld, F, out, limit);
     return last_err();
 }
 int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs& a) {
     if (a.rot_dims < 0 || (a.rot_dims & 1) || a.rot_dims > a.d || a.rot_dims > 4096) return -1000;
+    if (a.v_from_k && a.d != a.dv) return -1000;
     const size_t sm = (size_t)a.rot_dims * sizeof(float);
     if (a.kv_f32) attn_prep_kernel<float><<<rb.T, 256, sm, st>>>(rb, a);
     else attn_prep_kernel<bf16><<<rb.T, 256, sm, st>>>(rb, a);

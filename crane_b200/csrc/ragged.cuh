@@ -36,6 +36,14 @@ struct ActOut {
 enum LinearMode : int { LIN_STORE = 0, LIN_RESID = 1 };
 
 int embed_scale_rows_launch(cudaStream_t st, const int* ids, int T, const bf16* embed, int W, float scale, float* x, int ldx);
+// x[r, c] = embed[ids[r], c] + (c even ? sin : cos)(row_pos[r] * freq[c / 2]): the embedding row plus a sinusoidal position vector.
+// freq [ceil(W / 2)] radians per position; position and angle in f32
+int embed_sinpos_rows_launch(cudaStream_t st, const int* ids, const int* row_pos, int T, const bf16* embed, int W, const float* freq, float* x, int ldx);
+// Norm on a sublayer's way back into the stream.  One input: x[r] += rms(y1[r] + b1) * norm_w.  Two inputs (y2 != nullptr): each is
+// RMS-normed with its own weight first and half their sum takes y1's place: v = (rms(y1 + b1) * w1 + rms(y2) * w2) / 2.
+// b1, w1, w2 nullable.  Every mean of squares runs thread-strided, then over a fixed tree.
+int post_norm_add_launch(cudaStream_t st, const float* y1, int ld1, const float* b1, const float* w1, const float* y2, int ld2, const float* w2,
+                         const float* norm_w, float eps, float* x, int ldx, int T, int W);
 // out[r, c] = tanh(alpha * x[src(r), c]) * w[c] + b[c];  rows = gather list (nullptr: identity)
 int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w,
                     const float* b, const ActOut& out);
@@ -51,8 +59,8 @@ int store_rows_launch(cudaStream_t st, const float* src, int lds, int T, int W, 
 // the added value is also multiplied by sigmoid(gate[m, n] + gate_bias[n])
 int linear_f32_launch(cudaStream_t st, const float* A, int lda, const bf16* W, int ldw, int M, int N, int K, int mode, float* C, int ldc,
                       const float* col_scale = nullptr, const float* gate = nullptr, int ldg = 0, const float* gate_bias = nullptr);
-// out[r, j] = silu(gu[r, 2j]) * gu[r, 2j + 1]  (interleaved (gate, up) pairs)
-int silu_glu_launch(cudaStream_t st, const float* gu, int ld, int T, int F, const ActOut& out);
+// out[r, j] = silu(gu[r, 2j]) * gu[r, 2j + 1]  (interleaved (gate, up) pairs);  limit < 0: gelu_tanh in place of silu
+int silu_glu_launch(cudaStream_t st, const float* gu, int ld, int T, int F, const ActOut& out, float limit = 0.f);
 
 struct AttnPrepArgs {
     const float* qkv; int ld;         // [T, ld]: q heads | k heads | v heads (k / v absent when has_kv == 0)
@@ -69,6 +77,12 @@ struct AttnPrepArgs {
     int has_kv;
     const int* block_table; int max_pages;
     int no_norm = 0;                  // 1: queries and keys pass as they are (no RMS norm, no temperature); rotation still applies
+    const float* bias = nullptr;      // nullable [row width of qkv used]: added to every projected value before anything else
+    int whole_norm = 0;               // 1: ONE RMS statistic over all query heads of the row (and one over all key heads); the norm
+                                      //    weights then hold H * d (G * d) entries instead of d
+    int v_unit = 0;                   // 1: every value head is divided by its root mean square over dv (eps, no weight) before it is cached
+    int v_from_k = 0;                 // 1: the row has no value columns; the cached value of a head is its key as projected (+ bias), before the norm (dv == d)
+    const float* q_head_scale = nullptr;   // nullable [H]: head h's normalised query is multiplied by q_head_scale[h]
 };
 int attn_prep_launch(cudaStream_t st, const RaggedBatch& rb, const AttnPrepArgs& a);
 
@@ -84,6 +98,11 @@ struct SinkAttnArgs {
     ActOut out;                       // [T, H * dv]
     float* part; int nsplit;          // scratch [T, H, nsplit, dv + 2] when nsplit > 1
     int kv_shared = 0;                // 1: k_pool == v_pool and d == dv -- a cached row is its own value (staged once)
+    // score modifiers, applied in this order after the scale: s <- softcap * tanh(s / softcap) (softcap > 0);
+    // s <- s - dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (dist_r1 != nullptr);  s <- s + dist_table[min(i - j, dist_rows - 1) * H + h]
+    float softcap = 0.f;
+    const float* dist_r1 = nullptr; const float* dist_r2 = nullptr;
+    const float* dist_table = nullptr; int dist_rows = 0;
 };
 int sink_attention_launch(cudaStream_t st, const RaggedBatch& rb, const SinkAttnArgs& a);
 
@@ -165,6 +184,8 @@ struct CausalConvArgs {
     int add_input;
     ActOut out;
     int single_rows = 0;
+    const float* bias = nullptr;      // nullable [C]: added to the convolution's sum
+    int silu = 0;                     // 1: out = silu(sum) (after the bias)
 };
 int causal_conv_launch(cudaStream_t st, const RaggedBatch& rb, const CausalConvArgs& a);
 int causal_conv_launch_count(const CausalConvArgs& a);
@@ -217,6 +238,43 @@ int gla_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const GlaArgs& a);
 int gla_launch_count(bool has_seg_scratch, int max_len);
 size_t gla_seg_floats(int entries, int H, int d, int dv);
 size_t gla_seg_decay_offset(int entries, int H, int d, int dv);
+
+// Selective scan with a state per channel (Mamba-1).  u [T, ldu] the convolved, activated inputs (inner columns); low [T, ldl] holds
+// dt_low | B | C (dt_rank, N, N columns); z [T, ldz] the gate's pre-activations.  Per channel c and state n, all in f32:
+//   dt_c = softplus(w_dt[c, :] . dt_low + dt_b[c]);  S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n;  y_c = sum_n S[c, n] C_n + D_c u_c
+// out = y * silu(z).  The state [slots, inner, N] is carried in place.
+struct Mamba1Args {
+    const float* u; int ldu;
+    const float* low; int ldl;
+    const float* z; int ldz;
+    int inner, N, dt_rank;
+    const float* w_dt;                // [inner, dt_rank] f32
+    const float* dt_b;                // [inner]
+    const float* A;                   // [inner, N] f32, already -exp(A_log)
+    const float* D;                   // [inner]
+    float* state;
+    ActOut out;                       // [T, inner]
+};
+int mamba1_scan_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba1Args& a);
+
+// Matrix memory with exponential gates and a running maximum (mLSTM).  proj [T, ld] holds, from column col0 on,
+// q | k | v | g | i | f  (H*d, H*d, H*dv, H*dv, H, H columns).  Per head, all in f32, with c = gate_cap:
+//   ig = c tanh((i + i_b) / c);  fg = log sigmoid(c tanh((f + f_b) / c));  m_t = max(fg + m_(t-1), ig)
+//   S_t = exp(fg + m_(t-1) - m_t) S_(t-1) + exp(ig - m_t) k v^T;  n_t likewise from k;  o = S_t^T (q * q_scale) / (max(|n_t . q q_scale|, exp(-m_t)) + 1e-6)
+//   out = o / sqrt(mean_dv(o^2) + eps) * norm_w * sigmoid(g)
+// State per slot: S [slots, H, d, dv], n [slots, H, d], m [slots, H] (zeros for a new sequence), carried in place.
+struct MlstmArgs {
+    const float* proj; int ld; int col0;
+    int H, d, dv;
+    float gate_cap, q_scale, eps;
+    const float* i_b; const float* f_b;   // [H]
+    const float* norm_w;              // [H * dv]
+    float* S; float* n; float* m;
+    float* y;                         // [T, H * dv] scratch: S^T q before the division
+    float* gates;                     // [4, T, H] scratch: decay, input weight, exp(-m), n . q per token and head
+    ActOut out;                       // [T, H * dv]
+};
+int mlstm_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const MlstmArgs& a);
 
 // dst[r, c] = cap * tanh(src[r, c] / cap) for c < V (cap <= 0: a plain copy)
 int softcap_rows_launch(cudaStream_t st, const float* src, int lds, int R, int V, float cap, float* dst, int ldd);

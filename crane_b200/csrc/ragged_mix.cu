@@ -28,6 +28,8 @@ __global__ void causal_conv_rows_kernel(RaggedBatch rb, CausalConvArgs a) {
         const float u = back == 0 ? own : (i - back >= 0) ? a.in[(size_t)(r - back) * a.ld + c] : win[(size_t)(taps - 1 + i - back) * a.C + c];
         acc = fmaf(a.w[(size_t)c * taps + k], u, acc);
     }
+    if (a.bias) acc += a.bias[c];
+    if (a.silu) acc = acc / (1.f + __expf(-acc));
     store_act(a.out, r, c, a.add_input ? own + acc : acc);
 }
 // New window = the last taps - 1 inputs of the sequence (older ones shift down when the entry is shorter than the window).
@@ -56,6 +58,8 @@ __global__ void causal_conv_step_kernel(RaggedBatch rb, CausalConvArgs a) {
     }
     acc = fmaf(a.w[(size_t)c * taps + taps - 1], u, acc);
     if (taps > 1) win[(size_t)(taps - 2) * a.C + c] = u;
+    if (a.bias) acc += a.bias[c];
+    if (a.silu) acc = acc / (1.f + __expf(-acc));
     store_act(a.out, r, c, a.add_input ? u + acc : acc);
 }
 
