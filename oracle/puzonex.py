@@ -9,7 +9,7 @@ read the stream itself, and the norm sits on the way back:
 Notation (weights W are [out, in], applied as W x):
   rms(y, w)     = y / sqrt(mean(y^2) + eps) * w;      unit(y) = y / sqrt(mean(y^2) + eps)
   cap(s, c)     = c tanh(s / c)   (a configuration without "softcap" has no cap, one without "mask" no window)
-  position      : entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i), f_i = 10000^(-2i / width)
+  position      : entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i), f_i = 10000^(-2i / width); p, f_i and p f_i are float32 numbers
   attention     : q = W_q x + b_q, k = W_k x + b_k, v = W_v x + b_v;  q, k under rms per head (one weight vector of size dim shared
                   by the heads), v under unit() per head;  s_ij = cap(scale q_i . k_j) - r1_h ln(1 + r2_h (i - j));  keys with
                   0 <= i - j < window;  softmax whose denominator also holds exp(sink_h);  W_o on the heads
@@ -60,12 +60,14 @@ def silu(z):
 
 
 def position_vector(pos, width, dtype):
-    """pos [S] -> [S, width]: sines at the even entries, cosines of the same angles at the odd ones."""
+    """pos [S] -> [S, width]: sines at the even entries, cosines of the same angles at the odd ones.  Positions, frequencies and
+    their product (the angle) are float32 numbers, as the design has them; the sine and cosine of that angle are taken in `dtype`."""
     out = torch.zeros(len(pos), width, dtype=dtype)
-    p = torch.as_tensor(pos, dtype=dtype)
+    p = np.asarray(pos, dtype=np.float32)
     for c in range(width):
-        f = 10000.0 ** (-(2 * (c // 2)) / width)
-        out[:, c] = torch.sin(p * f) if c % 2 == 0 else torch.cos(p * f)
+        f = np.float32(10000.0 ** (-(2 * (c // 2)) / width))
+        ang = torch.from_numpy((p * f).astype(np.float32)).to(dtype)
+        out[:, c] = torch.sin(ang) if c % 2 == 0 else torch.cos(ang)
     return out
 
 
@@ -73,8 +75,8 @@ def bucket(n, rows, far):
     """Row of a learned distance table for the distance n >= 0: one row per distance up to rows / 2, then logarithmic steps that
     reach the last row at the distance `far`."""
     half = rows // 2
-    if n < half:
-        return n
+    if n < half or half == 0:
+        return min(n, rows - 1)
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
 
