@@ -699,6 +699,135 @@ def bench_nifarax(args, rank, world, local_rank):
     print(json.dumps(out))
 
 
+def bench_puzonex(args, rank, world, local_rank):
+    """The Puzonex layer-list decoder (sublayers normalised on their way back; Mamba-1, capped sink attention with a distance penalty,
+    windowed attention beside a matrix memory; tanh-GELU gated feed-forward) beside the closest existing model, a Fosovik stack with
+    Mamba-2 where Puzonex has a recurrent mixer and sink attention where it has attention, with a dense gated feed-forward, at equal
+    width, depth, heads and feed-forward width, at two sizes.  One request = 4096-token prefill + 256 greedy tokens through
+    `crane_b200_generate_greedy`; random bf16 blocks as weights (timing only; the small tensors are drawn properly); one GPU."""
+    import crane_b200
+    sys.path.insert(0, os.path.join(ROOT, "tools"))
+    import bench_configs as bc
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no model of this design"}))
+        return
+    if rank != 0:
+        return
+    S, n_dec = 4096, 256
+    peaks = load_peaks()
+    sampler = ClockSampler(0)
+
+    def closest(width, layers, heads, kv_heads, dim, r_heads, r_vdim, state, ff):
+        c = synth.fosovik_config(width=width, vocab=65536, blocks=1, attn_every=2, heads=heads, kv_heads=kv_heads, dim=dim, ssm_heads=r_heads,
+                                 ssm_vdim=r_vdim, state=state, groups=1, ff=ff)
+        rec, att = c["layers"]
+        c["layers"] = [dict(rec) if i % 3 == 0 else dict(att) for i in range(layers)]
+        return c
+    sizes = {
+        "w1024_12layers_ff3584": dict(
+            pzx=synth.puzonex_config(width=1024, layers=12, heads=8, kv_heads=2, dim=128, window=1024, inner=2048, state=16, dt_rank=64, mem_heads=4,
+                                     mem_dim=128, mem_vdim=256, ff=3584),
+            fsv=closest(1024, 12, 8, 2, 128, 16, 128, 16, 3584)),
+        "w2048_9layers_ff5632": dict(
+            pzx=synth.puzonex_config(width=2048, layers=9, heads=16, kv_heads=4, dim=128, window=2048, inner=4096, state=16, dt_rank=128, mem_heads=8,
+                                     mem_dim=128, mem_vdim=256, bias_max=2048, ff=5632),
+            fsv=closest(2048, 9, 16, 4, 128, 32, 128, 16, 5632)),
+    }
+
+    def load(cls, cfg):
+        m = cls(cfg, device=0, max_tokens=S + n_dec + 128, max_batch=4)
+        for name, shape, kind in synth.tensor_specs(cfg):
+            big = len(shape) == 2 and shape[0] * shape[1] >= (1 << 18) and kind in ("linear", "embed")
+            m.load_tensor(name, bc.cheap(shape, kind) if big else synth.make_tensor(name, shape, kind))
+        m.finalize()
+        return m
+
+    def work(cfg):
+        """(weights a token touches, attention / recurrence flops of the prompt, bytes of cache and state a decode step touches)"""
+        W, V = cfg["width"], cfg["vocab"]
+        shapes = {n: sh for n, sh, k in synth.tensor_specs(cfg)}
+        per_tok, attn_fl, cache_b = V * W, 0.0, 0.0
+        for i, L in enumerate(cfg["layers"]):
+            per_tok += sum(sh[0] * sh[1] for n, sh in shapes.items() if n.startswith(f"l{i}.") and len(sh) == 2 and ".mix.conv" not in n)
+            a = L["mixer"]
+
+            def attention(a):
+                keys = min(S / 2, a["mask"]["size"]) if a.get("mask") else S / 2
+                ctx = min(S + n_dec / 2, a["mask"]["size"]) if a.get("mask") else S + n_dec / 2
+                return 2.0 * S * keys * a["heads"] * (a["dim"] + a["vdim"]), ctx * a["kv_heads"] * (a["dim"] + a["vdim"]) * 4
+            if L["type"] == "attention":
+                f, b = attention(a)
+            elif L["type"] == "parallel":
+                f, b = attention(a["left"])
+                r = a["right"]
+                f += 4.0 * S * r["heads"] * r["dim"] * r["vdim"]
+                b += 2 * 4 * r["heads"] * r["dim"] * r["vdim"]
+            elif L["type"] == "mamba1":
+                f, b = 6.0 * S * a["inner"] * a["state"], 2 * 4 * a["inner"] * a["state"]
+            else:
+                f, b = 4.0 * S * a["heads"] * a["state"] * a["vdim"], 2 * 4 * a["heads"] * a["state"] * a["vdim"]
+            attn_fl += f
+            cache_b += b
+        return per_tok, attn_fl, cache_b
+
+    def measure(m, cfg, tag):
+        ids = synth.synth_token_ids(S, cfg["vocab"], tag)
+
+        def request():
+            m.clear_kv_cache()
+            t0 = time.perf_counter()
+            out = m.generate_greedy(ids, n_dec + 1)
+            wall = time.perf_counter() - t0
+            t = m.last_timing()
+            return wall, t["prefill_ms"], t["decode_ms"], len(out) - 1
+        for _ in range(max(args.warmup, 3)):
+            request()
+        l0 = m.kernel_launches()
+        rs = [request() for _ in range(args.steps)]
+        launches = m.kernel_launches() - l0
+        per_tok, attn_fl, cache_b = work(cfg)
+        W, V = cfg["width"], cfg["vocab"]
+        fl = 2.0 * (per_tok - V * W) * S + attn_fl + 2.0 * V * W
+        by = 2.0 * per_tok + cache_b
+        dec_s, ntok, pre_s = sum(r[2] for r in rs) / 1e3, sum(r[3] for r in rs), sum(r[1] for r in rs) / 1e3
+        return {"decode_tok_s": ntok / dec_s, "decode_us_per_step": 1e6 * dec_s / ntok, "prefill_ms": 1e3 * pre_s / len(rs),
+                "prefill_tok_s": S * len(rs) / pre_s, "prefill_tflops": fl * len(rs) / pre_s / 1e12,
+                "prefill_frac_of_bf16_peak": fl * len(rs) / pre_s / 1e12 / peaks["bf16_tflops"],
+                "decode_hbm_gbs": by / (dec_s / ntok) / 1e9, "decode_roofline_frac": by / (dec_s / ntok) / 1e9 / peaks["hbm_gbs"],
+                "algorithmic_bytes_per_step": by, "prefill_flop": fl, "e2e_tok_s": ntok / sum(r[0] for r in rs), "gpu_launches": int(launches)}
+
+    only = os.environ.get("CRANE_B200_BENCH_ONLY", "")          # "puzonex" / "closest": one side only (launch lists, profiles)
+    variants = {}
+    sampler.start()
+    for name, pair in sizes.items():
+        variants[name] = {}
+        for key, cls in (("puzonex", crane_b200.PuzonexModel), ("closest_model_fosovik", crane_b200.FosovikModel)):
+            if only and not key.startswith(only):
+                continue
+            cfg = pair["pzx" if key == "puzonex" else "fsv"]
+            m = load(cls, cfg)
+            variants[name][key] = measure(m, cfg, name + key)
+            m.close()
+        if only:
+            break
+    clocks = sampler.summary()
+    first = variants["w1024_12layers_ff3584"]
+    d = first.get("puzonex") or first["closest_model_fosovik"]
+    out = {"metric": "decode_tok_per_s", "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": f"Puzonex layer-list decoder (width 1024, 4 x (Mamba-1, attention beside a matrix memory, attention), window 1024, feed-forward 3584), {S}-token prefill + {n_dec} greedy decode tokens per request; the closest existing model at equal size beside it",
+                      "weights": "random bf16 blocks (timing only)", "l2": "per-token weight stream > 126 MB L2", "parallelism": "1 GPU",
+                      "precision": os.environ.get("CRANE_B200_PRECISION", "split")},
+           "value": d["decode_tok_s"], "ms_per_step": 1e3 / d["e2e_tok_s"] * n_dec, "prefill_ms": d["prefill_ms"], "prefill_tflops": d["prefill_tflops"],
+           "e2e": {"value": d["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": int(S * 4), "d2h_bytes_per_step": int((n_dec + 1) * 4),
+                   "api": "crane_b200_generate_greedy (host prompt ids in, host token ids out; prefill inside the timed region)"},
+           "gpu_launches": d["gpu_launches"], "clocks": clocks, "variants": variants,
+           "roofline": {"bound": "hbm", "achieved": d["decode_hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d["decode_roofline_frac"],
+                        "peak_source": peaks["source"], "launch": "one decode step (graph replay): the token's weights once + the windows' cached keys and values + recurrent states"}}
+    print(json.dumps(out))
+
+
 def other_config_summary(config, steps=2, timeout_s=120):
     """One more BASELINE config measured by THIS script in a child process (`bench.py --config <config>`), condensed for the headline
     line's `other_configs` field.  A child, so that nothing it does -- a failure, a hang (killed at the timeout) -- can keep the
@@ -727,7 +856,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="crane_b200", choices=["crane_b200", "reference"])
-    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b", "fosovik", "gavipel", "nifarax"])
+    ap.add_argument("--config", default="qwen3_vl_2b", choices=["qwen3_vl_2b", "tiny", "qwen3_8b_q4km", "qwen3_5_0_8b", "fosovik", "gavipel", "nifarax", "puzonex"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the config-2 (Qwen3.5-0.8B) child measurement appended to the headline line")
     args = ap.parse_args()
@@ -745,6 +874,8 @@ def main():
         return bench_gavipel(args, rank, world, local_rank)
     if args.config == "nifarax":
         return bench_nifarax(args, rank, world, local_rank)
+    if args.config == "puzonex":
+        return bench_puzonex(args, rank, world, local_rank)
     cfg = synth.QWEN3_VL_2B if args.config == "qwen3_vl_2b" else synth.TINY_QWEN3_VL
     name = "Qwen3-VL-2B" if args.config == "qwen3_vl_2b" else "tiny-Qwen3-VL"
     workload = f"{name} bf16, 1x(448x448) image + {N_TEXT}-tok prompt, prefill + {N_DECODE} greedy decode tokens per request"

@@ -519,7 +519,96 @@ def nifarax_tensor_specs(cfg: dict):
     yield "final.norm", (W,), "norm"
 
 
+def puzonex_config(width=1024, vocab=65536, layers=12, heads=8, kv_heads=2, dim=128, window=1024, softcap=30.0, inner=2048, state=16, dt_rank=64,
+                   conv=4, mem_heads=4, mem_dim=128, mem_vdim=256, gate_cap=15.0, rel_rows=32, bias_max=1024, ff=3584):
+    """`layers` layers in the order Mamba-1, attention beside a matrix memory, attention, ..., each with a tanh-GELU gated feed-forward.
+    `rel_rows` is not read by the engine (the distance table's rows come with its tensor); it tells `puzonex_tensor_specs` which
+    shape to make."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window}, "scale": dim ** -0.5, "softcap": softcap}
+    left = dict(att, bias_max=bias_max, rel_rows=rel_rows)
+    right = {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "gate_cap": gate_cap}
+    ssm = {"inner": inner, "state": state, "dt_rank": dt_rank, "conv": conv}
+    mlp = {"kind": "dense", "ff": ff} if ff else None
+    kinds = [("mamba1", ssm), ("parallel", {"left": left, "right": right}), ("attention", att)]
+    ls = [{"type": kinds[i % 3][0], "mixer": dict(kinds[i % 3][1]), "mlp": dict(mlp) if mlp else None} for i in range(layers)]
+    return {"architecture": "Puzonex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": ls}
+
+
+def puzonex_tensor_specs(cfg: dict):
+    """(name, shape, kind): 'embed', 'head', 'final.norm', 'l<i>.norm1|norm2', 'l<i>.mlp.gate|up|down', and per mixer
+    'l<i>.mix.q|q.b|k|k.b|v|v.b|q.norm|k.norm|r1|r2|sink|o', 'l<i>.mix.in|conv|conv.b|x|dt|dt.b|A_log|D|o', or
+    'l<i>.mix.left.q|q.b|k|k.b|q.norm|k.norm|rel|temp|g|o|o.b|out' with 'l<i>.mix.right.q|k|v|g|o|norm|i|i.b|f|f.b|out'."""
+    W, V = cfg["width"], cfg["vocab"]
+    yield "embed", (V, W), "embed"
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        yield p + "norm1", (W,), "norm"
+        if L["type"] == "attention":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            yield p + "mix.q", (H * d, W), "linear"
+            yield p + "mix.q.b", (H * d,), "bias"
+            yield p + "mix.k", (G * d, W), "linear"
+            yield p + "mix.k.b", (G * d,), "bias"
+            yield p + "mix.v", (G * dv, W), "linear"
+            yield p + "mix.v.b", (G * dv,), "bias"
+            yield p + "mix.q.norm", (d,), "norm"
+            yield p + "mix.k.norm", (d,), "norm"
+            yield p + "mix.r1", (H,), "rate"
+            yield p + "mix.r2", (H,), "rate"
+            yield p + "mix.sink", (H,), "bias"
+            yield p + "mix.o", (W, H * dv), "linear"
+        elif L["type"] == "mamba1":
+            I, N, R = m["inner"], m["state"], m["dt_rank"]
+            yield p + "mix.in", (2 * I, W), "linear"
+            yield p + "mix.conv", (I, m["conv"]), "linear"
+            yield p + "mix.conv.b", (I,), "bias"
+            yield p + "mix.x", (R + 2 * N, I), "linear"
+            yield p + "mix.dt", (I, R), "linear"
+            yield p + "mix.dt.b", (I,), "dt_bias"
+            yield p + "mix.A_log", (I, N), "a_log"
+            yield p + "mix.D", (I,), "norm"
+            yield p + "mix.o", (W, I), "linear"
+        else:
+            a, b = m["left"], m["right"]
+            H, G, d = a["heads"], a["kv_heads"], a["dim"]
+            yield p + "mix.left.q", (H * d, W), "linear"
+            yield p + "mix.left.q.b", (H * d,), "bias"
+            yield p + "mix.left.k", (G * d, W), "linear"
+            yield p + "mix.left.k.b", (G * d,), "bias"
+            yield p + "mix.left.q.norm", (H * d,), "norm"
+            yield p + "mix.left.k.norm", (G * d,), "norm"
+            yield p + "mix.left.rel", (a.get("rel_rows", 32), H), "bias"
+            yield p + "mix.left.temp", (H,), "norm"
+            yield p + "mix.left.g", (H * d, W), "linear"
+            yield p + "mix.left.o", (W, H * d), "linear"
+            yield p + "mix.left.o.b", (W,), "bias"
+            yield p + "mix.left.out", (W,), "norm"
+            yield p + "mix.right.out", (W,), "norm"
+            H, d, dv = b["heads"], b["dim"], b["vdim"]
+            yield p + "mix.right.q", (H * d, W), "linear"
+            yield p + "mix.right.k", (H * d, W), "linear"
+            yield p + "mix.right.v", (H * dv, W), "linear"
+            yield p + "mix.right.g", (H * dv, W), "linear"
+            yield p + "mix.right.o", (W, H * dv), "linear"
+            yield p + "mix.right.norm", (H * dv,), "norm"
+            yield p + "mix.right.i", (H, W), "linear"
+            yield p + "mix.right.i.b", (H,), "bias"
+            yield p + "mix.right.f", (H, W), "linear"
+            yield p + "mix.right.f.b", (H,), "forget_bias"
+        if L.get("mlp"):
+            F = L["mlp"]["ff"]
+            yield p + "norm2", (W,), "norm"
+            yield p + "mlp.gate", (F, W), "linear"
+            yield p + "mlp.up", (F, W), "linear"
+            yield p + "mlp.down", (W, F), "linear"
+    yield "final.norm", (W,), "norm"
+    yield "head", (V, W), "embed"
+
+
 def tensor_specs(cfg: dict):
+    if cfg.get("architecture") == "Puzonex":
+        yield from puzonex_tensor_specs(cfg)
+        return
     if cfg.get("architecture") == "Nifarax":
         yield from nifarax_tensor_specs(cfg)
         return
@@ -560,6 +649,10 @@ def make_tensor(name: str, shape, kind: str) -> np.ndarray:
         x = _normal(name, shape, 1.0)
     elif kind == "bias":
         x = _normal(name, shape, 0.02)
+    elif kind == "rate":       # positive numbers of a distance penalty
+        x = np.abs(_normal(name, shape, 0.2, 0.5))
+    elif kind == "forget_bias":    # forget gates that keep most of a memory
+        x = _normal(name, shape, 0.5, 4.0)
     elif kind == "alpha":      # Dynamic-Tanh slope: a scalar near one half
         x = _normal(name, shape, 0.02, 0.5)
     else:
