@@ -306,6 +306,9 @@ flash_prefill_kernel(FlashArgs a) {
     for (int i = 0; i < D / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
     float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
     const float sl2 = a.scale * 1.4426950408889634f;
+    const bool mods = CAUSAL && (a.softcap > 0.f || a.dist_r1 || a.dist_table);
+    const float dr1 = (CAUSAL && a.dist_r1) ? a.dist_r1[head] : 0.f, dr2 = (CAUSAL && a.dist_r1) ? a.dist_r2[head] : 0.f;
+    const float* dtab = (CAUSAL && a.dist_table) ? a.dist_table + (size_t)head * a.dist_rows : nullptr;
     uint32_t qf[SPLIT ? 1 : D / 16][4];        // plain mode keeps the Q fragments in registers; SPLIT re-reads them from smem
 
     bool first = true;
@@ -387,7 +390,15 @@ flash_prefill_kernel(FlashArgs a) {
                 const int col = kv0 + j * 8 + tq * 2 + (e & 1);
                 const int qrow = q0 + warp * 16 + g + (e >> 1) * 8;
                 const bool vis = (col < T) && (!CAUSAL || (col <= kv_off + qrow && (a.window <= 0 || kv_off + qrow - col < a.window)));
-                const float v = vis ? s_acc[j][e] * sl2 : -INFINITY;
+                float v = vis ? s_acc[j][e] * sl2 : -INFINITY;
+                if (CAUSAL && mods && vis) {          // cap, then the distance terms, in f32 on the scaled score
+                    float sc = s_acc[j][e] * a.scale;
+                    const int dist = kv_off + qrow - col;
+                    if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+                    if (a.dist_r1) sc -= dr1 * log1pf(dr2 * (float)dist);
+                    if (dtab) sc += dtab[min(dist, a.dist_rows - 1)];
+                    v = sc * 1.4426950408889634f;
+                }
                 s_acc[j][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }

@@ -60,6 +60,11 @@ struct FlashArgs {
     int window = 0;                     // causal mode, > 0: query i sees keys j with 0 <= i - j < window (key tiles before the window are skipped)
     const float* gate = nullptr;        // [rows, g_stride] f32, head h at h * D: out *= sigmoid(gate) before the store
     int g_stride = 0;
+    // causal mode, score modifiers in this order after the scale (f32): s <- softcap * tanh(s / softcap) (softcap > 0);
+    // s <- s - dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (dist_r1 != nullptr);  s <- s + dist_table[h * dist_rows + min(i - j, dist_rows - 1)]
+    float softcap = 0.f;
+    const float* dist_r1 = nullptr; const float* dist_r2 = nullptr;
+    const float* dist_table = nullptr; int dist_rows = 0;
 };
 
 // quantised KV pages <-> the bf16 (hi + lo) scratch the prefill kernels read and write (see prefill.cu)

@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) sink_attention_kernel(RaggedBa
                     float x = sc[q];
                     if (a.softcap > 0.f) x = a.softcap * tanhf(x / a.softcap);
                     if (a.dist_r1) x -= a.dist_r1[h0 + q] * log1pf(a.dist_r2[h0 + q] * (float)dist);
-                    if (a.dist_table) x += a.dist_table[(size_t)min(dist, a.dist_rows - 1) * a.H + h0 + q];
+                    if (a.dist_table) x += a.dist_table[(size_t)(h0 + q) * a.dist_rows + min(dist, a.dist_rows - 1)];
                     sc[q] = x;
                 }
             }

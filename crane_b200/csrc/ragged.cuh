@@ -99,7 +99,7 @@ struct SinkAttnArgs {
     float* part; int nsplit;          // scratch [T, H, nsplit, dv + 2] when nsplit > 1
     int kv_shared = 0;                // 1: k_pool == v_pool and d == dv -- a cached row is its own value (staged once)
     // score modifiers, applied in this order after the scale: s <- softcap * tanh(s / softcap) (softcap > 0);
-    // s <- s - dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (dist_r1 != nullptr);  s <- s + dist_table[min(i - j, dist_rows - 1) * H + h]
+    // s <- s - dist_r1[h] * ln(1 + dist_r2[h] * (i - j)) (dist_r1 != nullptr);  s <- s + dist_table[h * dist_rows + min(i - j, dist_rows - 1)]
     float softcap = 0.f;
     const float* dist_r1 = nullptr; const float* dist_r2 = nullptr;
     const float* dist_table = nullptr; int dist_rows = 0;
