@@ -307,6 +307,7 @@ flash_prefill_kernel(FlashArgs a) {
     float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
     const float sl2 = a.scale * 1.4426950408889634f;
     const bool mods = CAUSAL && (a.softcap > 0.f || a.dist_r1 || a.dist_table);
+    const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
     const float dr1 = (CAUSAL && a.dist_r1) ? a.dist_r1[head] : 0.f, dr2 = (CAUSAL && a.dist_r1) ? a.dist_r2[head] : 0.f;
     const float* dtab = (CAUSAL && a.dist_table) ? a.dist_table + (size_t)head * a.dist_rows : nullptr;
     uint32_t qf[SPLIT ? 1 : D / 16][4];        // plain mode keeps the Q fragments in registers; SPLIT re-reads them from smem
@@ -394,7 +395,10 @@ flash_prefill_kernel(FlashArgs a) {
                 if (CAUSAL && mods && vis) {          // cap, then the distance terms, in f32 on the scaled score
                     float sc = s_acc[j][e] * a.scale;
                     const int dist = kv_off + qrow - col;
-                    if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+                    if (a.softcap > 0.f) {            // tanh(x) = 1 - 2 / (e^{2x} + 1), with the hardware exponential and reciprocal (1e-7 of the cap)
+                        const float t = __expf(fminf(2.f * sc * inv_cap, 40.f));      // (tanh(20) is 1 to the last bit; no overflow into the reciprocal)
+                        sc = a.softcap * (1.f - __fdividef(2.f, t + 1.f));
+                    }
                     if (a.dist_r1) sc -= dr1 * log1pf(dr2 * (float)dist);
                     if (dtab) sc += dtab[min(dist, a.dist_rows - 1)];
                     v = sc * 1.4426950408889634f;

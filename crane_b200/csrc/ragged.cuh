@@ -248,8 +248,9 @@ struct Mamba1Args {
     const float* low; int ldl;
     const float* z; int ldz;
     int inner, N, dt_rank;
-    const float* w_dt;                // [inner, dt_rank] f32
+    const float* w_dtT;               // [dt_rank, inner] f32: the step sizes' projection, transposed
     const float* dt_b;                // [inner]
+    float* dt; int lddt;              // [T, lddt] scratch: the step sizes
     const float* A;                   // [inner, N] f32, already -exp(A_log)
     const float* D;                   // [inner]
     float* state;

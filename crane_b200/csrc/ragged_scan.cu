@@ -2,8 +2,8 @@
 //   * the selective scan with a state per channel (Mamba-1): decay exp(dt_c A[c, n]) per channel and state entry;
 //   * the matrix memory with exponential gates and a running maximum (mLSTM): a scalar decay per head and token.
 // Both walk a portion token by token; a thread keeps its share of the state in registers for the whole portion, the step inputs of
-// SC_CH tokens at a time are staged in shared memory, and everything that enters the recurrence (step sizes, softplus, decays,
-// gates, the running maximum) is computed in f32 when the chunk lands.  A row's result depends on its own sequence only: the
+// SC_CH tokens at a time are staged in shared memory (cp.async, double-buffered), and everything that enters the recurrence (step
+// sizes, softplus, decays, gates, the running maximum) is computed in f32.  A row's result depends on its own sequence only: the
 // split of the state over lanes and the order of the lane sums are launch constants.
 #include "ragged.cuh"
 #include "ragged_dev.cuh"
@@ -24,23 +24,61 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 // ---------------------------------------------------------------------------------------------------------------- Mamba-1
-// Block = (entry, SC_COLS channels); thread (cl, ns) owns the state entries n = ns * R .. ns * R + R - 1 of channel c0 + cl.
-// Staged per chunk: u [CH][COLS], dt [CH][COLS] (softplus of the low-rank projection, computed here), B and C [CH][NP].
+// Staged layout of a state vector of n entries cut into eight runs of R (one per lane of a channel): from R = 4 on every run is
+// followed by 4 pad floats, which spreads the eight runs of a warp over all banks and lets a lane read its run as float4.
+__host__ __device__ inline int sc_idx(int n, int R) { return R >= 4 ? n + 4 * (n / R) : n; }
+__host__ __device__ inline int sc_pad(int R) { return R >= 4 ? SC_NS * (R + 4) : SC_NS * R; }
+
+// Step sizes, block = (DT_TOK tokens, 128 channels): dt[t, c] = softplus(sum_k w_dt[c, k] low[t, k] + b[c]), k in order, f32.
+// w_dtT is the projection transposed, [dt_rank, inner]: a warp's channels read it side by side.
+template <int DT_TOK>
+__global__ void __launch_bounds__(128) mamba1_dt_kernel(Mamba1Args a, int T) {
+    extern __shared__ __align__(16) float slow[];             // [DT_TOK][dt_rank]
+    const int t0 = blockIdx.x * DT_TOK, c = blockIdx.y * 128 + threadIdx.x, Rk = a.dt_rank, nt = min(DT_TOK, T - t0);
+    for (int i = threadIdx.x; i < DT_TOK * Rk; i += 128) slow[i] = i / Rk < nt ? a.low[(size_t)(t0 + i / Rk) * a.ldl + i % Rk] : 0.f;
+    __syncthreads();
+    if (c >= a.inner) return;
+    float acc[DT_TOK];
+#pragma unroll
+    for (int t = 0; t < DT_TOK; ++t) acc[t] = 0.f;
+    const float* wc = a.w_dtT + c;
+    int k = 0;
+    for (; k + 8 <= Rk; k += 8) {                             // eight weights requested before the first is used
+        float w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) w[u] = wc[(size_t)(k + u) * a.inner];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int t = 0; t < DT_TOK; ++t) acc[t] = fmaf(w[u], slow[t * Rk + k + u], acc[t]);
+    }
+    for (; k < Rk; ++k) {
+        const float w = wc[(size_t)k * a.inner];
+#pragma unroll
+        for (int t = 0; t < DT_TOK; ++t) acc[t] = fmaf(w, slow[t * Rk + k], acc[t]);
+    }
+    const float b = a.dt_b[c];
+#pragma unroll
+    for (int t = 0; t < DT_TOK; ++t) if (t < nt) a.dt[(size_t)(t0 + t) * a.lddt + c] = softplus_f(acc[t] + b);
+}
+
+// Block = (entry, SC_COLS channels); thread (cl, ns) owns the state entries n = ns * R .. ns * R + R - 1 of channel c0 + cl in
+// registers for the whole portion.  The recurrence is one multiply-add deep per token; what would serialise it is the operand
+// fetch, so the step inputs of SC_CH tokens at a time (u, dt, z of the block's channels; B and C) are staged in shared memory with
+// cp.async, double-buffered: chunk c + 1 is in flight while chunk c is consumed.  A chunk's outputs wait in shared memory and leave
+// together, gated by silu(z).
 template <int R>
 __global__ void __launch_bounds__(SC_COLS * SC_NS) mamba1_scan_kernel(RaggedBatch rb, Mamba1Args a) {
     extern __shared__ __align__(16) float sm[];
     const int e = blockIdx.x, c0 = blockIdx.y * SC_COLS;
     const int ns = threadIdx.x & (SC_NS - 1), cl = threadIdx.x / SC_NS, c = c0 + cl;
-    const int N = a.N, NP = SC_NS * R, Rk = a.dt_rank;
+    const int N = a.N, NP = sc_pad(R), PT = 3 * SC_COLS + 2 * NP;       // per staged token: u | dt | z | B | C
     const bool live = c < a.inner;
     const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
-    float* su = sm;                         // [CH][COLS]
-    float* sdt = su + SC_CH * SC_COLS;      // [CH][COLS]
-    float* sB = sdt + SC_CH * SC_COLS;      // [CH][NP]
-    float* sC = sB + SC_CH * NP;            // [CH][NP]
-    float* slow = sC + SC_CH * NP;          // [CH][Rk]
-    float* swdt = slow + SC_CH * Rk;        // [COLS][Rk]
-    const int n0 = ns * R;
+    float* stage[2] = {sm, sm + SC_CH * PT};
+    float* sy = sm + 2 * SC_CH * PT;                                    // [CH][COLS]
+    const int n0 = ns * R, ncol = min(SC_COLS, a.inner - c0);
+    for (int i = threadIdx.x; i < 2 * SC_CH * PT; i += blockDim.x) sm[i] = 0.f;       // entries past N, channels past the last stay zero
     float s[R], An[R];
     float* S = a.state + ((size_t)slot * a.inner + (live ? c : 0)) * N;
 #pragma unroll
@@ -49,51 +87,83 @@ __global__ void __launch_bounds__(SC_COLS * SC_NS) mamba1_scan_kernel(RaggedBatc
         s[i] = ok ? S[n0 + i] : 0.f;
         An[i] = ok ? a.A[(size_t)c * N + n0 + i] : 0.f;
     }
-    for (int i = threadIdx.x; i < SC_COLS * Rk; i += blockDim.x) {
-        const int cc = c0 + i / Rk;
-        swdt[i] = cc < a.inner ? a.w_dt[(size_t)cc * Rk + i % Rk] : 0.f;
-    }
     const float Dc = live ? a.D[c] : 0.f;
-    for (int t0 = 0; t0 < len; t0 += SC_CH) {
-        const int nt = min(SC_CH, len - t0);
-        __syncthreads();                    // the last chunk's readers are done
-        for (int i = threadIdx.x; i < nt * SC_COLS; i += blockDim.x) {
-            const int t = i / SC_COLS, cc = c0 + i % SC_COLS;
-            su[i] = cc < a.inner ? a.u[(size_t)(r0 + t0 + t) * a.ldu + cc] : 0.f;
+    __syncthreads();
+    // 16-byte copies when every piece starts on a 16-byte boundary (the usual geometry), 4-byte copies otherwise
+    const bool wide = ((N | a.dt_rank | a.inner | a.ldu | a.ldl | a.ldz | a.lddt) & 3) == 0 && (R >= 4 ? (R & 3) == 0 : true) && ncol == SC_COLS &&
+                      (((size_t)a.u | (size_t)a.low | (size_t)a.z | (size_t)a.dt) & 15) == 0;
+    auto fetch = [&](int ch, float* dst) {
+        const int t0 = ch * SC_CH, nt = min(SC_CH, len - t0);
+        if (wide) {
+            const int nq = N >> 2, per = 12 + 2 * nq;
+            for (int i = threadIdx.x; i < nt * per; i += blockDim.x) {
+                const int t = i / per, k = i - t * per, r = r0 + t0 + t;
+                float* d0 = dst + t * PT;
+                if (k < 4) cp_async16s(d0 + 4 * k, a.u + (size_t)r * a.ldu + c0 + 4 * k);
+                else if (k < 8) cp_async16s(d0 + SC_COLS + 4 * (k - 4), a.dt + (size_t)r * a.lddt + c0 + 4 * (k - 4));
+                else if (k < 12) cp_async16s(d0 + 2 * SC_COLS + 4 * (k - 8), a.z + (size_t)r * a.ldz + c0 + 4 * (k - 8));
+                else if (k < 12 + nq) { const int n = 4 * (k - 12); cp_async16s(d0 + 3 * SC_COLS + sc_idx(n, R), a.low + (size_t)r * a.ldl + a.dt_rank + n); }
+                else { const int n = 4 * (k - 12 - nq); cp_async16s(d0 + 3 * SC_COLS + NP + sc_idx(n, R), a.low + (size_t)r * a.ldl + a.dt_rank + N + n); }
+            }
+        } else {
+            const int per = 3 * SC_COLS + 2 * N;
+            for (int i = threadIdx.x; i < nt * per; i += blockDim.x) {
+                const int t = i / per, k = i - t * per, r = r0 + t0 + t;
+                float* d0 = dst + t * PT;
+                if (k < 3 * SC_COLS) {
+                    const int which = k / SC_COLS, cc = k % SC_COLS;
+                    if (cc >= ncol) continue;
+                    const float* src = which == 0 ? a.u + (size_t)r * a.ldu : which == 1 ? a.dt + (size_t)r * a.lddt : a.z + (size_t)r * a.ldz;
+                    cp_async4(d0 + k, src + c0 + cc);
+                } else if (k < 3 * SC_COLS + N) { const int n = k - 3 * SC_COLS; cp_async4(d0 + 3 * SC_COLS + sc_idx(n, R), a.low + (size_t)r * a.ldl + a.dt_rank + n); }
+                else { const int n = k - 3 * SC_COLS - N; cp_async4(d0 + 3 * SC_COLS + NP + sc_idx(n, R), a.low + (size_t)r * a.ldl + a.dt_rank + N + n); }
+            }
         }
-        for (int i = threadIdx.x; i < nt * NP; i += blockDim.x) {
-            const int t = i / NP, n = i % NP;
-            const float* lr = a.low + (size_t)(r0 + t0 + t) * a.ldl + Rk;
-            sB[i] = n < N ? lr[n] : 0.f;
-            sC[i] = n < N ? lr[N + n] : 0.f;
-        }
-        for (int i = threadIdx.x; i < nt * Rk; i += blockDim.x) slow[i] = a.low[(size_t)(r0 + t0 + i / Rk) * a.ldl + i % Rk];
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nch = (len + SC_CH - 1) / SC_CH;
+    fetch(0, stage[0]);
+    for (int ch = 0; ch < nch; ++ch) {
+        if (ch + 1 < nch) { fetch(ch + 1, stage[(ch + 1) & 1]); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * SC_COLS; i += blockDim.x) {       // step sizes: a dt_rank-long dot per (token, channel), in order
-            const int t = i / SC_COLS, cc = i % SC_COLS;
-            float z = 0.f;
-            for (int k = 0; k < Rk; ++k) z = fmaf(swdt[cc * Rk + k], slow[t * Rk + k], z);
-            sdt[i] = c0 + cc < a.inner ? softplus_f(z + a.dt_b[c0 + cc]) : 0.f;
-        }
-        __syncthreads();
+        const float* st = stage[ch & 1];
+        const int nt = min(SC_CH, len - ch * SC_CH);
         for (int t = 0; t < nt; ++t) {
-            const float dt = sdt[t * SC_COLS + cl], uv = su[t * SC_COLS + cl], dx = dt * uv;
-            const float* Bt = sB + t * NP + n0;
-            const float* Ct = sC + t * NP + n0;
+            const float* tk = st + t * PT;
+            const float uv = tk[cl], dt = tk[SC_COLS + cl], dx = dt * uv;
+            const float* Bt = tk + 3 * SC_COLS + sc_idx(n0, R);
+            const float* Ct = Bt + NP;
             float y = 0.f;
+            if constexpr ((R & 3) == 0) {
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                s[i] = fmaf(__expf(dt * An[i]), s[i], dx * Bt[i]);
-                y = fmaf(s[i], Ct[i], y);
+                for (int i = 0; i < R / 4; ++i) {
+                    const float4 b = reinterpret_cast<const float4*>(Bt)[i], cc = reinterpret_cast<const float4*>(Ct)[i];
+                    s[4 * i] = fmaf(__expf(dt * An[4 * i]), s[4 * i], dx * b.x); y = fmaf(s[4 * i], cc.x, y);
+                    s[4 * i + 1] = fmaf(__expf(dt * An[4 * i + 1]), s[4 * i + 1], dx * b.y); y = fmaf(s[4 * i + 1], cc.y, y);
+                    s[4 * i + 2] = fmaf(__expf(dt * An[4 * i + 2]), s[4 * i + 2], dx * b.z); y = fmaf(s[4 * i + 2], cc.z, y);
+                    s[4 * i + 3] = fmaf(__expf(dt * An[4 * i + 3]), s[4 * i + 3], dx * b.w); y = fmaf(s[4 * i + 3], cc.w, y);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    s[i] = fmaf(__expf(dt * An[i]), s[i], dx * Bt[i]);
+                    y = fmaf(s[i], Ct[i], y);
+                }
             }
 #pragma unroll
             for (int o = SC_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (ns == 0 && live) {
-                const int r = r0 + t0 + t;
-                const float zz = a.z[(size_t)r * a.ldz + c];
-                store_act(a.out, r, c, (y + Dc * uv) * (zz / (1.f + expf(-zz))));
+            if (ns == 0) sy[t * SC_COLS + cl] = y + Dc * uv;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * SC_COLS; i += blockDim.x) {      // the chunk's outputs, gated
+            const int t = i / SC_COLS, cc = i % SC_COLS;
+            if (cc < ncol) {
+                const float zz = st[t * PT + 2 * SC_COLS + cc];
+                store_act(a.out, r0 + ch * SC_CH + t, c0 + cc, sy[i] * (zz / (1.f + expf(-zz))));
             }
         }
+        __syncthreads();                                      // the stage is free for chunk ch + 2
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) if (live && n0 + i < N) S[n0 + i] = s[i];
@@ -140,64 +210,103 @@ __global__ void __launch_bounds__(MG_CH) mlstm_gates_kernel(RaggedBatch rb, Mlst
     if (threadIdx.x == 0) a.m[(size_t)slot * H + h] = m_run;
 }
 
-// The memory itself, block = (entry, head, SC_COLS columns); thread (pl, ns) owns rows n0 .. n0 + R - 1 of column p0 + pl.  Columns
-// 0 .. dv - 1 are those of S; column dv is the normaliser n (a value column whose value is always 1), kept in its own array.
-// Staged per chunk: q (scaled), k [CH][DP], v [CH][COLS], decay and input weight per token.  The products S^T q and n . q go to
-// scratch; mlstm_out_kernel divides, normalises and gates.
+// The memory itself, block = (entry, head, SC_COLS columns); thread (pl, ns) owns rows n0 .. n0 + R - 1 of column p0 + pl in
+// registers.  Columns 0 .. dv - 1 are those of S; column dv is the normaliser n (a value column whose value is always 1), kept in its
+// own array.  Staged per chunk with cp.async, double-buffered: q, k (padded runs, see sc_idx), the block's value columns, decay and
+// input weight per token.  The products S^T q and n . q of a chunk wait in shared memory and leave together; mlstm_out_kernel divides,
+// normalises and gates.
 template <int R>
 __global__ void __launch_bounds__(SC_COLS * SC_NS) mlstm_scan_kernel(RaggedBatch rb, MlstmArgs a, int T) {
     extern __shared__ __align__(16) float sm[];
-    __shared__ float sa[SC_CH], sb[SC_CH];
     const int e = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * SC_COLS;
     const int ns = threadIdx.x & (SC_NS - 1), pl = threadIdx.x / SC_NS, p = p0 + pl;
-    const int H = a.H, d = a.d, dv = a.dv, DP = SC_NS * R;
+    const int H = a.H, d = a.d, dv = a.dv, DP = sc_pad(R), PT = 2 * DP + SC_COLS + 4;      // per staged token: q | k | v | decay, input weight
     const bool live = p <= dv, is_n = p == dv;
     const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
-    float* sq = sm;                         // [CH][DP]
-    float* sk = sq + SC_CH * DP;            // [CH][DP]
-    float* sv = sk + SC_CH * DP;            // [CH][COLS]
+    float* stage[2] = {sm, sm + SC_CH * PT};
+    float* sy = sm + 2 * SC_CH * PT;                        // [CH][COLS]
+    for (int i = threadIdx.x; i < 2 * SC_CH * PT; i += blockDim.x) sm[i] = 0.f;        // rows past d and columns past dv stay zero
     const int n0 = ns * R;
-    float* col = is_n ? a.n + ((size_t)slot * H + h) * d : a.S + ((size_t)slot * H + h) * d * dv + p;      // this thread's column, row stride cs
+    float* col = is_n ? a.n + ((size_t)slot * H + h) * d : a.S + ((size_t)slot * H + h) * d * dv + (live ? p : 0);      // this thread's column, row stride cs
     const size_t cs = is_n ? 1 : (size_t)dv;
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) s[i] = (live && n0 + i < d) ? col[(size_t)(n0 + i) * cs] : 0.f;
     const int qc = a.col0 + h * d, kc = a.col0 + H * d + h * d, vc = a.col0 + 2 * H * d + h * dv;
-    for (int t0 = 0; t0 < len; t0 += SC_CH) {
-        const int nt = min(SC_CH, len - t0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * DP; i += blockDim.x) {
-            const int t = i / DP, n = i % DP;
-            const float* row = a.proj + (size_t)(r0 + t0 + t) * a.ld;
-            sq[i] = n < d ? row[qc + n] * a.q_scale : 0.f;
-            sk[i] = n < d ? row[kc + n] : 0.f;
-        }
-        for (int i = threadIdx.x; i < nt * SC_COLS; i += blockDim.x) {
-            const int t = i / SC_COLS, pp = p0 + i % SC_COLS;
-            sv[i] = pp < dv ? a.proj[(size_t)(r0 + t0 + t) * a.ld + vc + pp] : pp == dv ? 1.f : 0.f;
-        }
-        if (threadIdx.x < nt) {
-            const float* g = a.gates + (size_t)(r0 + t0 + threadIdx.x) * H + h;
-            sa[threadIdx.x] = g[0]; sb[threadIdx.x] = g[(size_t)T * H];
-        }
-        __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float dec = sa[t], bv = sb[t] * sv[t * SC_COLS + pl];
-            const float* kt = sk + t * DP + n0;
-            const float* qt = sq + t * DP + n0;
-            float y = 0.f;
-#pragma unroll
-            for (int i = 0; i < R; ++i) {
-                s[i] = fmaf(dec, s[i], bv * kt[i]);
-                y = fmaf(s[i], qt[i], y);
+    const int ncol = max(0, min(SC_COLS, dv - p0));          // value columns of S in this block
+    __syncthreads();
+    const bool wide = ((d | dv | a.ld | a.col0) & 3) == 0 && (R & 3) == 0 && ((size_t)a.proj & 15) == 0;
+    auto fetch = [&](int ch, float* dst) {
+        const int t0 = ch * SC_CH, nt = min(SC_CH, len - t0);
+        if (wide) {
+            const int nq = d >> 2, nv = ncol >> 2, per = 2 * nq + nv;
+            for (int i = threadIdx.x; i < nt * per; i += blockDim.x) {
+                const int t = i / per, k = i - t * per;
+                const float* row = a.proj + (size_t)(r0 + t0 + t) * a.ld;
+                float* d0 = dst + t * PT;
+                if (k < nq) cp_async16s(d0 + sc_idx(4 * k, R), row + qc + 4 * k);
+                else if (k < 2 * nq) cp_async16s(d0 + DP + sc_idx(4 * (k - nq), R), row + kc + 4 * (k - nq));
+                else cp_async16s(d0 + 2 * DP + 4 * (k - 2 * nq), row + vc + p0 + 4 * (k - 2 * nq));
             }
+        } else {
+            const int per = 2 * d + ncol;
+            for (int i = threadIdx.x; i < nt * per; i += blockDim.x) {
+                const int t = i / per, k = i - t * per;
+                const float* row = a.proj + (size_t)(r0 + t0 + t) * a.ld;
+                float* d0 = dst + t * PT;
+                if (k < d) cp_async4(d0 + sc_idx(k, R), row + qc + k);
+                else if (k < 2 * d) cp_async4(d0 + DP + sc_idx(k - d, R), row + kc + k - d);
+                else cp_async4(d0 + 2 * DP + k - 2 * d, row + vc + p0 + k - 2 * d);
+            }
+        }
+        if (threadIdx.x < 2 * nt) {
+            const int t = threadIdx.x >> 1, w = threadIdx.x & 1;
+            cp_async4(dst + t * PT + 2 * DP + SC_COLS + w, a.gates + (size_t)w * T * H + (size_t)(r0 + t0 + t) * H + h);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nch = (len + SC_CH - 1) / SC_CH;
+    fetch(0, stage[0]);
+    for (int ch = 0; ch < nch; ++ch) {
+        if (ch + 1 < nch) { fetch(ch + 1, stage[(ch + 1) & 1]); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float* st = stage[ch & 1];
+        const int nt = min(SC_CH, len - ch * SC_CH);
+        for (int t = 0; t < nt; ++t) {
+            const float* tk = st + t * PT;
+            const float dec = tk[2 * DP + SC_COLS], bv = tk[2 * DP + SC_COLS + 1] * (is_n ? 1.f : tk[2 * DP + pl]);
+            const float* qt = tk + sc_idx(n0, R);
+            const float* kt = qt + DP;
+            float y0 = 0.f, y1 = 0.f;
+            if constexpr ((R & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < R / 4; ++i) {
+                    const float4 kk = reinterpret_cast<const float4*>(kt)[i], qq = reinterpret_cast<const float4*>(qt)[i];
+                    s[4 * i] = fmaf(dec, s[4 * i], bv * kk.x); y0 = fmaf(s[4 * i], qq.x, y0);
+                    s[4 * i + 1] = fmaf(dec, s[4 * i + 1], bv * kk.y); y1 = fmaf(s[4 * i + 1], qq.y, y1);
+                    s[4 * i + 2] = fmaf(dec, s[4 * i + 2], bv * kk.z); y0 = fmaf(s[4 * i + 2], qq.z, y0);
+                    s[4 * i + 3] = fmaf(dec, s[4 * i + 3], bv * kk.w); y1 = fmaf(s[4 * i + 3], qq.w, y1);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    s[i] = fmaf(dec, s[i], bv * kt[i]);
+                    y0 = fmaf(s[i], qt[i], y0);
+                }
+            }
+            float y = y0 + y1;
 #pragma unroll
             for (int o = SC_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (ns == 0 && live) {
-                if (is_n) a.gates[(size_t)3 * T * H + (size_t)(r0 + t0 + t) * H + h] = y;
-                else a.y[(size_t)(r0 + t0 + t) * H * dv + h * dv + p] = y;
-            }
+            if (ns == 0) sy[t * SC_COLS + pl] = y * a.q_scale;
         }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * SC_COLS; i += blockDim.x) {
+            const int t = i / SC_COLS, pp = p0 + i % SC_COLS, r = r0 + ch * SC_CH + t;
+            if (pp < dv) a.y[(size_t)r * H * dv + h * dv + pp] = sy[i];
+            else if (pp == dv) a.gates[(size_t)3 * T * H + (size_t)r * H + h] = sy[i];
+        }
+        __syncthreads();                                      // the stage is free for chunk ch + 2
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) if (live && n0 + i < d) col[(size_t)(n0 + i) * cs] = s[i];
@@ -221,10 +330,20 @@ __global__ void mlstm_out_kernel(MlstmArgs a, int T) {
 }  // namespace
 
 int mamba1_scan_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba1Args& a) {
-    if (a.inner < 1 || a.N < 1 || a.N > SC_NS * 32 || a.dt_rank < 1) return -1000;
+    if (a.inner < 1 || a.N < 1 || a.N > SC_NS * 32 || a.dt_rank < 1 || !a.dt || !a.w_dtT) return -1000;
+    static SmemOptIn seen_dt, seen_dt1;
+    if (rb.T <= 8) {            // a decode step: one token per block row, so that every channel block of every token is a block of its own
+        const size_t dsm = (size_t)a.dt_rank * sizeof(float);
+        if (const int er = ensure_dyn_smem(mamba1_dt_kernel<1>, dsm, seen_dt1)) return er;
+        mamba1_dt_kernel<1><<<dim3(rb.T, (a.inner + 127) / 128), 128, dsm, st>>>(a, rb.T);
+    } else {
+        const size_t dsm = (size_t)32 * a.dt_rank * sizeof(float);
+        if (const int er = ensure_dyn_smem(mamba1_dt_kernel<32>, dsm, seen_dt)) return er;
+        mamba1_dt_kernel<32><<<dim3((rb.T + 31) / 32, (a.inner + 127) / 128), 128, dsm, st>>>(a, rb.T);
+    }
+    if (const int er = last_err()) return er;
     const int nr = (a.N + SC_NS - 1) / SC_NS, R = nr <= 1 ? 1 : nr <= 2 ? 2 : nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
-    const size_t smem = (size_t)(2 * SC_CH * SC_COLS + 2 * SC_CH * SC_NS * R + SC_CH * a.dt_rank + SC_COLS * a.dt_rank) * sizeof(float);
-    if (smem > 200 * 1024) return -1000;
+    const size_t smem = (size_t)(2 * SC_CH * (3 * SC_COLS + 2 * sc_pad(R)) + SC_CH * SC_COLS) * sizeof(float);
     const dim3 grid(rb.E, (a.inner + SC_COLS - 1) / SC_COLS);
     auto run = [&](auto kern, SmemOptIn& seen) -> int {
         if (const int er = ensure_dyn_smem(kern, smem, seen)) return er;
@@ -249,7 +368,7 @@ int mlstm_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const MlstmArgs& 
     int e = last_err();
     if (e) return e;
     const int nr = (a.d + SC_NS - 1) / SC_NS, R = nr <= 2 ? 2 : nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
-    const size_t smem = (size_t)(2 * SC_CH * SC_NS * R + SC_CH * SC_COLS) * sizeof(float);
+    const size_t smem = (size_t)(2 * SC_CH * (2 * sc_pad(R) + SC_COLS + 4) + SC_CH * SC_COLS) * sizeof(float);
     const dim3 grid(rb.E, a.H, (a.dv + 1 + SC_COLS - 1) / SC_COLS);
     auto run = [&](auto kern, SmemOptIn& seen) -> int {
         if (const int er = ensure_dyn_smem(kern, smem, seen)) return er;
