@@ -255,8 +255,15 @@ struct Mamba1Args {
     const float* D;                   // [inner]
     float* state;
     ActOut out;                       // [T, inner]
+    // long portions run as segments side by side (see ragged_scan.cu): scratch for their local / start states and step-size sums,
+    // mamba1_seg_floats(entries, ...) floats in all; nullptr = never segment
+    float* seg_state = nullptr; float* seg_dt = nullptr;
+    int max_len = 0;                  // rows of the longest entry
 };
 int mamba1_scan_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba1Args& a);
+int mamba1_launch_count(bool has_seg_scratch, int max_len);
+size_t mamba1_seg_floats(int entries, int inner, int N);
+size_t mamba1_seg_dt_offset(int entries, int inner, int N);
 
 // Matrix memory with exponential gates and a running maximum (mLSTM).  proj [T, ld] holds, from column col0 on,
 // q | k | v | g | i | f  (H*d, H*d, H*dv, H*dv, H, H columns).  Per head, all in f32, with c = gate_cap:
@@ -274,8 +281,15 @@ struct MlstmArgs {
     float* y;                         // [T, H * dv] scratch: S^T q before the division
     float* gates;                     // [4, T, H] scratch: decay, input weight, exp(-m), n . q per token and head
     ActOut out;                       // [T, H * dv]
+    // long portions run as segments side by side: scratch for their local / start states ([d, dv + 1] per head, the normaliser as
+    // the last column) and decay products, mlstm_seg_floats(entries, ...) floats in all; nullptr = never segment
+    float* seg_state = nullptr; float* seg_decay = nullptr;
+    int max_len = 0;                  // rows of the longest entry
 };
 int mlstm_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const MlstmArgs& a);
+int mlstm_launch_count(bool has_seg_scratch, int max_len);
+size_t mlstm_seg_floats(int entries, int H, int d, int dv);
+size_t mlstm_seg_decay_offset(int entries, int H, int d, int dv);
 
 // dst[r, c] = cap * tanh(src[r, c] / cap) for c < V (cap <= 0: a plain copy)
 int softcap_rows_launch(cudaStream_t st, const float* src, int lds, int R, int V, float cap, float* dst, int ldd);

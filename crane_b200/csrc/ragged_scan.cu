@@ -9,6 +9,7 @@
 #include "ragged_dev.cuh"
 
 #include <algorithm>
+#include <type_traits>
 
 namespace cb {
 
@@ -17,6 +18,14 @@ namespace {
 constexpr int SC_NS = 8;        // lanes that share one channel (Mamba-1) / one value column (mLSTM): each owns a contiguous slice of the state
 constexpr int SC_COLS = 16;     // channels / value columns per block -> 128 threads
 constexpr int SC_CH = 16;       // tokens staged per chunk
+// A long portion is cut into SC_SEGS segments that run side by side (a scan has one resident warp per scheduler and waits on its
+// own dependent chain most of the time).  Both recurrences are linear in the state with a decay that does not depend on it, so
+//   S_end(segment) = (product of the segment's decays) * S_start + S_local(segment run from zero),
+// element by element.  MODE 1 runs every segment but the last from zero and leaves S_local and what the decay product needs;
+// a prefix kernel turns them into each segment's start state; MODE 2 is the scan proper from those start states (the last segment
+// leaves the sequence's new state).  MODE 0 = one segment, everything.
+constexpr int SC_SEGS = 4, SC_SEG_MIN = 512;          // segmented from this many rows in the step's longest entry
+__host__ __device__ inline int sc_seg_len(int len) { return ((len + SC_SEGS - 1) / SC_SEGS + SC_CH - 1) / SC_CH * SC_CH; }
 
 inline int last_err() { return (int)cudaGetLastError(); }
 
@@ -67,26 +76,33 @@ __global__ void __launch_bounds__(128) mamba1_dt_kernel(Mamba1Args a, int T) {
 // fetch, so the step inputs of SC_CH tokens at a time (u, dt, z of the block's channels; B and C) are staged in shared memory with
 // cp.async, double-buffered: chunk c + 1 is in flight while chunk c is consumed.  A chunk's outputs wait in shared memory and leave
 // together, gated by silu(z).
-template <int R>
+template <int R, int MODE>
 __global__ void __launch_bounds__(SC_COLS * SC_NS) mamba1_scan_kernel(RaggedBatch rb, Mamba1Args a) {
     extern __shared__ __align__(16) float sm[];
-    const int e = blockIdx.x, c0 = blockIdx.y * SC_COLS;
+    const int e = MODE == 0 ? blockIdx.x : blockIdx.x / SC_SEGS, seg = MODE == 0 ? 0 : blockIdx.x % SC_SEGS, c0 = blockIdx.y * SC_COLS;
     const int ns = threadIdx.x & (SC_NS - 1), cl = threadIdx.x / SC_NS, c = c0 + cl;
     const int N = a.N, NP = sc_pad(R), PT = 3 * SC_COLS + 2 * NP;       // per staged token: u | dt | z | B | C
     const bool live = c < a.inner;
-    const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
+    const int full_len = rb.ent_len[e], slot = rb.ent_slot[e];
+    const int seg_len = MODE == 0 ? full_len : sc_seg_len(full_len), seg0 = seg * seg_len;
+    if (seg0 >= full_len) return;                             // (a short entry has fewer segments)
+    const bool last_seg = seg0 + seg_len >= full_len;
+    if (MODE == 1 && last_seg) return;                        // nothing follows the last segment: its end state is MODE 2's to leave
+    const int len = min(seg_len, full_len - seg0), r0 = rb.ent_row0[e] + seg0;
     float* stage[2] = {sm, sm + SC_CH * PT};
     float* sy = sm + 2 * SC_CH * PT;                                    // [CH][COLS]
     const int n0 = ns * R, ncol = min(SC_COLS, a.inner - c0);
     for (int i = threadIdx.x; i < 2 * SC_CH * PT; i += blockDim.x) sm[i] = 0.f;       // entries past N, channels past the last stay zero
     float s[R], An[R];
     float* S = a.state + ((size_t)slot * a.inner + (live ? c : 0)) * N;
+    float* Sg = MODE == 0 ? S : a.seg_state + (((size_t)e * SC_SEGS + seg) * a.inner + (live ? c : 0)) * N;      // MODE 1 leaves S_local here, MODE 2 starts from it
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const bool ok = live && n0 + i < N;
-        s[i] = ok ? S[n0 + i] : 0.f;
+        s[i] = (ok && MODE != 1) ? Sg[n0 + i] : 0.f;
         An[i] = ok ? a.A[(size_t)c * N + n0 + i] : 0.f;
     }
+    float dt_sum = 0.f;                                       // MODE 1: the segment's decay product is exp(A * sum of its step sizes)
     const float Dc = live ? a.D[c] : 0.f;
     __syncthreads();
     // 16-byte copies when every piece starts on a 16-byte boundary (the usual geometry), 4-byte copies otherwise
@@ -129,9 +145,11 @@ __global__ void __launch_bounds__(SC_COLS * SC_NS) mamba1_scan_kernel(RaggedBatc
         __syncthreads();
         const float* st = stage[ch & 1];
         const int nt = min(SC_CH, len - ch * SC_CH);
-        for (int t = 0; t < nt; ++t) {
+        const int tmax = (nt + 3) & ~3;                       // whole groups of four: a token past the end leaves the state as it is
+#pragma unroll 4
+        for (int t = 0; t < tmax; ++t) {
             const float* tk = st + t * PT;
-            const float uv = tk[cl], dt = tk[SC_COLS + cl], dx = dt * uv;
+            const float uv = tk[cl], dt = t < nt ? tk[SC_COLS + cl] : 0.f, dx = dt * uv;
             const float* Bt = tk + 3 * SC_COLS + sc_idx(n0, R);
             const float* Ct = Bt + NP;
             float y = 0.f;
@@ -153,10 +171,11 @@ __global__ void __launch_bounds__(SC_COLS * SC_NS) mamba1_scan_kernel(RaggedBatc
             }
 #pragma unroll
             for (int o = SC_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (ns == 0) sy[t * SC_COLS + cl] = y + Dc * uv;
+            if (MODE == 1) dt_sum += dt;
+            if (MODE != 1 && ns == 0) sy[t * SC_COLS + cl] = y + Dc * uv;
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * SC_COLS; i += blockDim.x) {      // the chunk's outputs, gated
+        for (int i = threadIdx.x; i < (MODE == 1 ? 0 : nt * SC_COLS); i += blockDim.x) {      // the chunk's outputs, gated
             const int t = i / SC_COLS, cc = i % SC_COLS;
             if (cc < ncol) {
                 const float zz = st[t * PT + 2 * SC_COLS + cc];
@@ -165,8 +184,28 @@ __global__ void __launch_bounds__(SC_COLS * SC_NS) mamba1_scan_kernel(RaggedBatc
         }
         __syncthreads();                                      // the stage is free for chunk ch + 2
     }
+    float* Sout = MODE == 1 ? Sg : S;                         // MODE 0 and the last segment of MODE 2: the sequence's new state
+    if (MODE == 2 && !last_seg) return;
 #pragma unroll
-    for (int i = 0; i < R; ++i) if (live && n0 + i < N) S[n0 + i] = s[i];
+    for (int i = 0; i < R; ++i) if (live && n0 + i < N) Sout[n0 + i] = s[i];
+    if (MODE == 1 && ns == 0 && live) a.seg_dt[((size_t)e * SC_SEGS + seg) * a.inner + c] = dt_sum;
+}
+// Start state of every segment, in order: seg_state[k] holds S_local on entry and S_start(k) on exit (the last segment's end state is
+// left by the scan proper).
+__global__ void mamba1_seg_prefix_kernel(RaggedBatch rb, Mamba1Args a) {
+    const int e = blockIdx.x, N = a.N, total = a.inner * N;
+    const int len = rb.ent_len[e], slot = rb.ent_slot[e], nseg = (len + sc_seg_len(len) - 1) / sc_seg_len(len);
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < total; i += gridDim.y * blockDim.x) {
+        const int c = i / N;
+        float cur = a.state[(size_t)slot * total + i];
+        const float An = a.A[i];
+        for (int k = 0; k < nseg; ++k) {
+            float* loc = a.seg_state + ((size_t)e * SC_SEGS + k) * total + i;
+            const float l = *loc;
+            *loc = cur;
+            if (k + 1 < nseg) cur = fmaf(__expf(An * a.seg_dt[((size_t)e * SC_SEGS + k) * a.inner + c]), cur, l);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------- mLSTM
@@ -215,23 +254,32 @@ __global__ void __launch_bounds__(MG_CH) mlstm_gates_kernel(RaggedBatch rb, Mlst
 // own array.  Staged per chunk with cp.async, double-buffered: q, k (padded runs, see sc_idx), the block's value columns, decay and
 // input weight per token.  The products S^T q and n . q of a chunk wait in shared memory and leave together; mlstm_out_kernel divides,
 // normalises and gates.
-template <int R>
+template <int R, int MODE>
 __global__ void __launch_bounds__(SC_COLS * SC_NS) mlstm_scan_kernel(RaggedBatch rb, MlstmArgs a, int T) {
     extern __shared__ __align__(16) float sm[];
-    const int e = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * SC_COLS;
+    const int e = MODE == 0 ? blockIdx.x : blockIdx.x / SC_SEGS, seg = MODE == 0 ? 0 : blockIdx.x % SC_SEGS, h = blockIdx.y, p0 = blockIdx.z * SC_COLS;
     const int ns = threadIdx.x & (SC_NS - 1), pl = threadIdx.x / SC_NS, p = p0 + pl;
     const int H = a.H, d = a.d, dv = a.dv, DP = sc_pad(R), PT = 2 * DP + SC_COLS + 4;      // per staged token: q | k | v | decay, input weight
     const bool live = p <= dv, is_n = p == dv;
-    const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
+    const int full_len = rb.ent_len[e], slot = rb.ent_slot[e];
+    const int seg_len = MODE == 0 ? full_len : sc_seg_len(full_len), seg0 = seg * seg_len;
+    if (seg0 >= full_len) return;                             // (a short entry has fewer segments)
+    const bool last_seg = seg0 + seg_len >= full_len;
+    if (MODE == 1 && last_seg) return;                        // nothing follows the last segment: its end state is MODE 2's to leave
+    const int len = min(seg_len, full_len - seg0), r0 = rb.ent_row0[e] + seg0;
     float* stage[2] = {sm, sm + SC_CH * PT};
     float* sy = sm + 2 * SC_CH * PT;                        // [CH][COLS]
     for (int i = threadIdx.x; i < 2 * SC_CH * PT; i += blockDim.x) sm[i] = 0.f;        // rows past d and columns past dv stay zero
     const int n0 = ns * R;
     float* col = is_n ? a.n + ((size_t)slot * H + h) * d : a.S + ((size_t)slot * H + h) * d * dv + (live ? p : 0);      // this thread's column, row stride cs
     const size_t cs = is_n ? 1 : (size_t)dv;
+    // segments keep their states as [d, dv + 1] per head (the normaliser is column dv): MODE 1 leaves S_local there, MODE 2 starts from it
+    float* gcol = MODE == 0 ? col : a.seg_state + (((size_t)e * SC_SEGS + seg) * H + h) * d * (dv + 1) + (live ? p : 0);
+    const size_t gs = MODE == 0 ? cs : (size_t)(dv + 1);
     float s[R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) s[i] = (live && n0 + i < d) ? col[(size_t)(n0 + i) * cs] : 0.f;
+    for (int i = 0; i < R; ++i) s[i] = (live && n0 + i < d && MODE != 1) ? gcol[(size_t)(n0 + i) * gs] : 0.f;
+    float dprod = 1.f;                                        // MODE 1: product of the segment's decays
     const int qc = a.col0 + h * d, kc = a.col0 + H * d + h * d, vc = a.col0 + 2 * H * d + h * dv;
     const int ncol = max(0, min(SC_COLS, dv - p0));          // value columns of S in this block
     __syncthreads();
@@ -273,9 +321,11 @@ __global__ void __launch_bounds__(SC_COLS * SC_NS) mlstm_scan_kernel(RaggedBatch
         __syncthreads();
         const float* st = stage[ch & 1];
         const int nt = min(SC_CH, len - ch * SC_CH);
-        for (int t = 0; t < nt; ++t) {
+        const int tmax = (nt + 3) & ~3;                       // whole groups of four: a token past the end leaves the memory as it is
+#pragma unroll 4
+        for (int t = 0; t < tmax; ++t) {
             const float* tk = st + t * PT;
-            const float dec = tk[2 * DP + SC_COLS], bv = tk[2 * DP + SC_COLS + 1] * (is_n ? 1.f : tk[2 * DP + pl]);
+            const float dec = t < nt ? tk[2 * DP + SC_COLS] : 1.f, bv = t < nt ? tk[2 * DP + SC_COLS + 1] * (is_n ? 1.f : tk[2 * DP + pl]) : 0.f;
             const float* qt = tk + sc_idx(n0, R);
             const float* kt = qt + DP;
             float y0 = 0.f, y1 = 0.f;
@@ -295,21 +345,42 @@ __global__ void __launch_bounds__(SC_COLS * SC_NS) mlstm_scan_kernel(RaggedBatch
                     y0 = fmaf(s[i], qt[i], y0);
                 }
             }
+            if (MODE == 1) { dprod *= dec; continue; }
             float y = y0 + y1;
 #pragma unroll
             for (int o = SC_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
             if (ns == 0) sy[t * SC_COLS + pl] = y * a.q_scale;
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * SC_COLS; i += blockDim.x) {
+        for (int i = threadIdx.x; i < (MODE == 1 ? 0 : nt * SC_COLS); i += blockDim.x) {
             const int t = i / SC_COLS, pp = p0 + i % SC_COLS, r = r0 + ch * SC_CH + t;
             if (pp < dv) a.y[(size_t)r * H * dv + h * dv + pp] = sy[i];
             else if (pp == dv) a.gates[(size_t)3 * T * H + (size_t)r * H + h] = sy[i];
         }
         __syncthreads();                                      // the stage is free for chunk ch + 2
     }
+    if (MODE == 2 && !last_seg) return;
+    float* ocol = MODE == 1 ? gcol : col;                     // MODE 0 and the last segment of MODE 2: the sequence's new memory
+    const size_t os = MODE == 1 ? gs : cs;
 #pragma unroll
-    for (int i = 0; i < R; ++i) if (live && n0 + i < d) col[(size_t)(n0 + i) * cs] = s[i];
+    for (int i = 0; i < R; ++i) if (live && n0 + i < d) ocol[(size_t)(n0 + i) * os] = s[i];
+    if (MODE == 1 && threadIdx.x == 0 && blockIdx.z == 0) a.seg_decay[((size_t)e * SC_SEGS + seg) * H + h] = dprod;
+}
+// Start state of every segment, in order: seg_state[k] holds S_local on entry and S_start(k) on exit (the last segment's end state is
+// left by the scan proper).
+__global__ void mlstm_seg_prefix_kernel(RaggedBatch rb, MlstmArgs a) {
+    const int e = blockIdx.x, h = blockIdx.y, d = a.d, dv = a.dv, np = d * (dv + 1);
+    const int len = rb.ent_len[e], slot = rb.ent_slot[e], nseg = (len + sc_seg_len(len) - 1) / sc_seg_len(len);
+    for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < np; i += gridDim.z * blockDim.x) {
+        const int row = i / (dv + 1), p = i % (dv + 1);
+        float cur = p == dv ? a.n[((size_t)slot * a.H + h) * d + row] : a.S[(((size_t)slot * a.H + h) * d + row) * dv + p];
+        for (int k = 0; k < nseg; ++k) {
+            float* loc = a.seg_state + (((size_t)e * SC_SEGS + k) * a.H + h) * np + i;
+            const float l = *loc;
+            *loc = cur;
+            if (k + 1 < nseg) cur = fmaf(a.seg_decay[((size_t)e * SC_SEGS + k) * a.H + h], cur, l);
+        }
+    }
 }
 
 // o = (S^T q) / (max(|n . q|, exp(-m)) + 1e-6);  out = o / sqrt(mean_dv(o^2) + eps) * norm_w * sigmoid(g): one warp per (row, head)
@@ -344,22 +415,34 @@ int mamba1_scan_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba1Args&
     if (const int er = last_err()) return er;
     const int nr = (a.N + SC_NS - 1) / SC_NS, R = nr <= 1 ? 1 : nr <= 2 ? 2 : nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
     const size_t smem = (size_t)(2 * SC_CH * (3 * SC_COLS + 2 * sc_pad(R)) + SC_CH * SC_COLS) * sizeof(float);
-    const dim3 grid(rb.E, (a.inner + SC_COLS - 1) / SC_COLS);
+    const bool segs = a.seg_state != nullptr && a.max_len >= SC_SEG_MIN;
+    const dim3 grid(segs ? rb.E * SC_SEGS : rb.E, (a.inner + SC_COLS - 1) / SC_COLS);
     auto run = [&](auto kern, SmemOptIn& seen) -> int {
         if (const int er = ensure_dyn_smem(kern, smem, seen)) return er;
         kern<<<grid, SC_COLS * SC_NS, smem, st>>>(rb, a);
         return last_err();
     };
-    static SmemOptIn seen[6];
-    switch (R) {
-        case 1: return run(mamba1_scan_kernel<1>, seen[0]);
-        case 2: return run(mamba1_scan_kernel<2>, seen[1]);
-        case 4: return run(mamba1_scan_kernel<4>, seen[2]);
-        case 8: return run(mamba1_scan_kernel<8>, seen[3]);
-        case 16: return run(mamba1_scan_kernel<16>, seen[4]);
-        default: return run(mamba1_scan_kernel<32>, seen[5]);
-    }
+    static SmemOptIn seen[3][6];
+    auto scan = [&](auto mode) -> int {
+        constexpr int M = decltype(mode)::value;
+        switch (R) {
+            case 1: return run(mamba1_scan_kernel<1, M>, seen[M][0]);
+            case 2: return run(mamba1_scan_kernel<2, M>, seen[M][1]);
+            case 4: return run(mamba1_scan_kernel<4, M>, seen[M][2]);
+            case 8: return run(mamba1_scan_kernel<8, M>, seen[M][3]);
+            case 16: return run(mamba1_scan_kernel<16, M>, seen[M][4]);
+            default: return run(mamba1_scan_kernel<32, M>, seen[M][5]);
+        }
+    };
+    if (!segs) return scan(std::integral_constant<int, 0>{});
+    if (const int er = scan(std::integral_constant<int, 1>{})) return er;
+    mamba1_seg_prefix_kernel<<<dim3(rb.E, 16), 256, 0, st>>>(rb, a);
+    if (const int er = last_err()) return er;
+    return scan(std::integral_constant<int, 2>{});
 }
+int mamba1_launch_count(bool has_seg_scratch, int max_len) { return (has_seg_scratch && max_len >= SC_SEG_MIN) ? 4 : 2; }
+size_t mamba1_seg_floats(int entries, int inner, int N) { return (size_t)entries * SC_SEGS * inner * ((size_t)N + 1); }
+size_t mamba1_seg_dt_offset(int entries, int inner, int N) { return (size_t)entries * SC_SEGS * inner * (size_t)N; }
 
 int mlstm_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const MlstmArgs& a) {
     if (a.H < 1 || a.d < 1 || a.d > SC_NS * 32 || a.dv < 1 || !(a.gate_cap > 0.f) || !a.gates) return -1000;
@@ -369,24 +452,38 @@ int mlstm_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const MlstmArgs& 
     if (e) return e;
     const int nr = (a.d + SC_NS - 1) / SC_NS, R = nr <= 2 ? 2 : nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32;
     const size_t smem = (size_t)(2 * SC_CH * (2 * sc_pad(R) + SC_COLS + 4) + SC_CH * SC_COLS) * sizeof(float);
-    const dim3 grid(rb.E, a.H, (a.dv + 1 + SC_COLS - 1) / SC_COLS);
+    const bool segs = a.seg_state != nullptr && a.max_len >= SC_SEG_MIN;
+    const dim3 grid(segs ? rb.E * SC_SEGS : rb.E, a.H, (a.dv + 1 + SC_COLS - 1) / SC_COLS);
     auto run = [&](auto kern, SmemOptIn& seen) -> int {
         if (const int er = ensure_dyn_smem(kern, smem, seen)) return er;
         kern<<<grid, SC_COLS * SC_NS, smem, st>>>(rb, a, T);
         return last_err();
     };
-    static SmemOptIn seen[5];
-    switch (R) {
-        case 2: e = run(mlstm_scan_kernel<2>, seen[0]); break;
-        case 4: e = run(mlstm_scan_kernel<4>, seen[1]); break;
-        case 8: e = run(mlstm_scan_kernel<8>, seen[2]); break;
-        case 16: e = run(mlstm_scan_kernel<16>, seen[3]); break;
-        default: e = run(mlstm_scan_kernel<32>, seen[4]); break;
+    static SmemOptIn seen[3][5];
+    auto scan = [&](auto mode) -> int {
+        constexpr int M = decltype(mode)::value;
+        switch (R) {
+            case 2: return run(mlstm_scan_kernel<2, M>, seen[M][0]);
+            case 4: return run(mlstm_scan_kernel<4, M>, seen[M][1]);
+            case 8: return run(mlstm_scan_kernel<8, M>, seen[M][2]);
+            case 16: return run(mlstm_scan_kernel<16, M>, seen[M][3]);
+            default: return run(mlstm_scan_kernel<32, M>, seen[M][4]);
+        }
+    };
+    if (!segs) e = scan(std::integral_constant<int, 0>{});
+    else {
+        if ((e = scan(std::integral_constant<int, 1>{}))) return e;
+        mlstm_seg_prefix_kernel<<<dim3(rb.E, a.H, 8), 256, 0, st>>>(rb, a);
+        if ((e = last_err())) return e;
+        e = scan(std::integral_constant<int, 2>{});
     }
     if (e) return e;
     const int warps = T * a.H;
     mlstm_out_kernel<<<(warps + 3) / 4, 128, 0, st>>>(a, T);
     return last_err();
 }
+int mlstm_launch_count(bool has_seg_scratch, int max_len) { return (has_seg_scratch && max_len >= SC_SEG_MIN) ? 5 : 3; }
+size_t mlstm_seg_floats(int entries, int H, int d, int dv) { return (size_t)entries * SC_SEGS * H * ((size_t)d * (dv + 1) + 1); }
+size_t mlstm_seg_decay_offset(int entries, int H, int d, int dv) { return (size_t)entries * SC_SEGS * H * (size_t)d * (dv + 1); }
 
 }  // namespace cb

@@ -191,7 +191,7 @@ CRANE_B200_API int crane_b200_decode_batch(crane_b200_model* m, const int* seqs,
  * how much): every entry brings the next n_tokens of one sequence -- a portion of a prompt, cut anywhere, or one decoded token --
  * and all entries run as ONE batch over the weights, each sequence on its own KV pages and recurrent-state slot.  `want` lists the
  * positions among an entry's tokens whose logits are computed; the result rows follow the order of the entries and of `want`
- * (crane_b200_copy_logits copies rows * vocab floats).  Layer-list models ("architecture" in config.json: "Fosovik", "Gavipel", "Nifarax") run this
+ * (crane_b200_copy_logits copies rows * vocab floats).  Layer-list models ("architecture" in config.json: "Fosovik", "Gavipel", "Nifarax", "Puzonex") run this
  * natively; their KV pages come from one pool of engine.max_tokens tokens (64 per page) that sequences draw from as they grow and
  * return to with seq_free / clear_kv_cache, and engine.max_batch sequence slots hold the recurrent state.
  * "engine": {"max_tokens": N, "max_batch": B, "precision": "split"|"bf16"|"f32"} -- "f32" runs every product in true 32-bit. */

@@ -351,6 +351,27 @@ def test_keys_far_away_without_a_window():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("precision,tol", [("f32", F32_TOL), ("split", SPLIT_TOL)])
+def test_long_portions_scan_in_segments(precision, tol):
+    # from 512 rows on a portion's recurrences run as four segments side by side; here on carried states, beside a short request,
+    # with lengths that leave the last segment ragged, a state width that is not a multiple of four and a one-segment entry
+    cfg = config([layer(mamba1(inner=72, state=6, dt_rank=5, conv=3), None),
+                  layer(parallel(heads=2, kv_heads=1, dim=16, window=50, rheads=2, rdim=18, rvdim=21, gate_cap=6.0), 40),
+                  layer(mamba1(inner=64, state=16, dt_rank=8, conv=4), None)], width=96, vocab=150)
+    m, w = make(cfg, 27, precision=precision, max_tokens=2048)
+    ids, other = tokens(1400, cfg["vocab"], 28), tokens(40, cfg["vocab"], 29)
+    want, want2 = oracle_logits(cfg, w, ids), oracle_logits(cfg, w, other)
+    s1 = m.seq_create()
+    a = m.step_batch([(0, ids[:100], [99])])
+    b = m.step_batch([(s1, other[:30], [29]), (0, ids[100:803], [0, 350, 702])])
+    c = m.step_batch([(0, ids[803:1399], [0, 595]), (s1, other[30:], [9])])
+    d = m.step_batch([(0, ids[1399:], [0])])
+    assert rel(np.concatenate([a, b[1:], c[:2], d]), want[[99, 100, 450, 802, 803, 1398, 1399]]) < tol
+    assert rel(np.stack([b[0], c[2]]), want2[[29, 39]]) < tol
+    m.close()
+
+
+@pytest.mark.gpu
 def test_first_tokens_of_a_sequence():
     m, w = make(FULL, 15, precision="f32")
     ids = tokens(7, FULL["vocab"], 16)
