@@ -214,7 +214,7 @@ __global__ void mamba1_seg_prefix_kernel(RaggedBatch rb, Mamba1Args a) {
 // thread, the exponentials follow side by side.  Only this kernel reads and writes the carried maximum.
 constexpr int MG_CH = 256;
 __global__ void __launch_bounds__(MG_CH) mlstm_gates_kernel(RaggedBatch rb, MlstmArgs a, int T) {
-    __shared__ float sig[MG_CH], sfg[MG_CH], sa[MG_CH], sb[MG_CH], sem[MG_CH];
+    __shared__ float sig[MG_CH], sfg[MG_CH], sem[MG_CH + 1];
     __shared__ float m_run;
     const int e = blockIdx.x, h = blockIdx.y, H = a.H;
     const int len = rb.ent_len[e], r0 = rb.ent_row0[e], slot = rb.ent_slot[e];
@@ -230,19 +230,21 @@ __global__ void __launch_bounds__(MG_CH) mlstm_gates_kernel(RaggedBatch rb, Mlst
             sfg[t] = log_sigmoid_f(a.gate_cap * tanhf((row[fc] + fb) / a.gate_cap));
         }
         __syncthreads();
-        if (t == 0) {
+        if (t == 0) {                       // the chain itself: one addition and one comparison per token
             float m = m_run;
+            sem[MG_CH] = m;
+#pragma unroll 8
             for (int k = 0; k < nt; ++k) {
-                const float mn = fmaxf(sfg[k] + m, sig[k]);
-                sa[k] = sfg[k] + m - mn; sb[k] = sig[k] - mn; sem[k] = -mn;
-                m = mn;
+                m = fmaxf(sfg[k] + m, sig[k]);
+                sem[k] = m;
             }
             m_run = m;
         }
         __syncthreads();
-        if (t < nt) {
+        if (t < nt) {                       // what follows from it, side by side (the same roundings as a token-by-token walk: fg + m, then the difference)
+            const float m_prev = t ? sem[t - 1] : sem[MG_CH], m_new = sem[t];
             float* g = a.gates + (size_t)(r0 + t0 + t) * H + h;
-            g[0] = expf(sa[t]); g[(size_t)T * H] = expf(sb[t]); g[(size_t)2 * T * H] = expf(sem[t]);
+            g[0] = expf((sfg[t] + m_prev) - m_new); g[(size_t)T * H] = expf(sig[t] - m_new); g[(size_t)2 * T * H] = expf(-m_new);
         }
     }
     __syncthreads();
