@@ -36,7 +36,7 @@ __global__ void embed_sinpos_rows_kernel(const int* __restrict__ ids, const int*
 // Block per row.  One input: x += rms(y1 + b1) * norm_w.  Two inputs: v = (rms(y1 + b1) * w1 + rms(y2) * w2) / 2, x += rms(v) * norm_w.
 __global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restrict__ y1, int ld1, const float* __restrict__ b1, const float* __restrict__ w1,
                                                             const float* __restrict__ y2, int ld2, const float* __restrict__ w2,
-                                                            const float* __restrict__ norm_w, float eps, float* __restrict__ x, int ldx, int W) {
+                                                            const float* __restrict__ norm_w, float eps, float* __restrict__ x, int ldx, int W, ActOut planes) {
     __shared__ float red[3][8];
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* a = y1 + (size_t)r * ld1;
@@ -59,7 +59,11 @@ __global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restr
     }
     const float ia = 1.f / sqrtf(total(sa, 0) / (float)W + eps);
     if (!b) {
-        for (int c = threadIdx.x; c < W; c += 256) xr[c] += (a[c] + (b1 ? b1[c] : 0.f)) * ia * norm_w[c];
+        for (int c = threadIdx.x; c < W; c += 256) {
+            const float nx = xr[c] + (a[c] + (b1 ? b1[c] : 0.f)) * ia * norm_w[c];
+            xr[c] = nx;
+            store_act(planes, r, c, nx);
+        }
         return;
     }
     const float ib = 1.f / sqrtf(total(sb, 1) / (float)W + eps);
@@ -71,7 +75,9 @@ __global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restr
     const float iv = 1.f / sqrtf(total(sv, 2) / (float)W + eps);
     for (int c = threadIdx.x; c < W; c += 256) {
         const float v = 0.5f * ((a[c] + (b1 ? b1[c] : 0.f)) * ia * (w1 ? w1[c] : 1.f) + b[c] * ib * (w2 ? w2[c] : 1.f));
-        xr[c] += v * iv * norm_w[c];
+        const float nx = xr[c] + v * iv * norm_w[c];
+        xr[c] = nx;
+        store_act(planes, r, c, nx);
     }
 }
 
@@ -1082,9 +1088,9 @@ int embed_sinpos_rows_launch(cudaStream_t st, const int* ids, const int* row_pos
     return last_err();
 }
 int post_norm_add_launch(cudaStream_t st, const float* y1, int ld1, const float* b1, const float* w1, const float* y2, int ld2, const float* w2,
-                         const float* norm_w, float eps, float* x, int ldx, int T, int W) {
-    if (!y1 || !norm_w) return -1000;
-    post_norm_add_kernel<<<T, 256, 0, st>>>(y1, ld1, b1, w1, y2, ld2, w2, norm_w, eps, x, ldx, W);
+                         const float* norm_w, float eps, float* x, int ldx, int T, int W, const ActOut& planes) {
+    if (!y1 || !norm_w || planes.f) return -1000;
+    post_norm_add_kernel<<<T, 256, 0, st>>>(y1, ld1, b1, w1, y2, ld2, w2, norm_w, eps, x, ldx, W, planes);
     return last_err();
 }
 int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w, const float* b,

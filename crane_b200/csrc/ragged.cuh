@@ -41,9 +41,10 @@ int embed_scale_rows_launch(cudaStream_t st, const int* ids, int T, const bf16* 
 int embed_sinpos_rows_launch(cudaStream_t st, const int* ids, const int* row_pos, int T, const bf16* embed, int W, const float* freq, float* x, int ldx);
 // Norm on a sublayer's way back into the stream.  One input: x[r] += rms(y1[r] + b1) * norm_w.  Two inputs (y2 != nullptr): each is
 // RMS-normed with its own weight first and half their sum takes y1's place: v = (rms(y1 + b1) * w1 + rms(y2) * w2) / 2.
-// b1, w1, w2 nullable.  Every mean of squares runs thread-strided, then over a fixed tree.
+// b1, w1, w2 nullable.  Every mean of squares runs thread-strided, then over a fixed tree.  planes (optional): the new x also leaves as
+// bf16 operand planes, for the linear that reads the stream next.
 int post_norm_add_launch(cudaStream_t st, const float* y1, int ld1, const float* b1, const float* w1, const float* y2, int ld2, const float* w2,
-                         const float* norm_w, float eps, float* x, int ldx, int T, int W);
+                         const float* norm_w, float eps, float* x, int ldx, int T, int W, const ActOut& planes = ActOut{});
 // out[r, c] = tanh(alpha * x[src(r), c]) * w[c] + b[c];  rows = gather list (nullptr: identity)
 int dyt_rows_launch(cudaStream_t st, const float* x, int ldx, const int* rows, int R, int W, const float* alpha, const float* w,
                     const float* b, const ActOut& out);

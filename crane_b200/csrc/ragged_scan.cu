@@ -24,7 +24,7 @@ constexpr int SC_CH = 16;       // tokens staged per chunk
 // element by element.  MODE 1 runs every segment but the last from zero and leaves S_local and what the decay product needs;
 // a prefix kernel turns them into each segment's start state; MODE 2 is the scan proper from those start states (the last segment
 // leaves the sequence's new state).  MODE 0 = one segment, everything.
-constexpr int SC_SEGS = 4, SC_SEG_MIN = 512;          // segmented from this many rows in the step's longest entry
+constexpr int SC_SEGS = 8, SC_SEG_MIN = 512;          // segmented from this many rows in the step's longest entry
 __host__ __device__ inline int sc_seg_len(int len) { return ((len + SC_SEGS - 1) / SC_SEGS + SC_CH - 1) / SC_CH * SC_CH; }
 
 inline int last_err() { return (int)cudaGetLastError(); }
@@ -438,7 +438,7 @@ int mamba1_scan_launch(cudaStream_t st, const RaggedBatch& rb, const Mamba1Args&
     };
     if (!segs) return scan(std::integral_constant<int, 0>{});
     if (const int er = scan(std::integral_constant<int, 1>{})) return er;
-    mamba1_seg_prefix_kernel<<<dim3(rb.E, 16), 256, 0, st>>>(rb, a);
+    mamba1_seg_prefix_kernel<<<dim3(rb.E, std::max(1, std::min(128, (a.inner * a.N + 255) / 256))), 256, 0, st>>>(rb, a);
     if (const int er = last_err()) return er;
     return scan(std::integral_constant<int, 2>{});
 }
@@ -475,7 +475,7 @@ int mlstm_mixer_launch(cudaStream_t st, const RaggedBatch& rb, const MlstmArgs& 
     if (!segs) e = scan(std::integral_constant<int, 0>{});
     else {
         if ((e = scan(std::integral_constant<int, 1>{}))) return e;
-        mlstm_seg_prefix_kernel<<<dim3(rb.E, a.H, 8), 256, 0, st>>>(rb, a);
+        mlstm_seg_prefix_kernel<<<dim3(rb.E, a.H, std::max(1, std::min(64, (a.d * (a.dv + 1) + 255) / 256))), 256, 0, st>>>(rb, a);
         if ((e = last_err())) return e;
         e = scan(std::integral_constant<int, 2>{});
     }
