@@ -424,7 +424,7 @@ def test_greedy_generation_through_generate_and_the_scheduler():
 @pytest.mark.gpu
 def test_wide_layers_take_the_tensor_core_paths():
     # widths the tensor-core kernels take: 64- and 128-wide heads, many rows; a wide scan state and a 128 x 64 matrix memory
-    cfg = config([layer(attention(heads=4, kv_heads=2, dim=64, vdim=64, window=100, scale=0.12), 320),
+    cfg = config([layer(attention(heads=4, kv_heads=2, dim=64, vdim=64, window=100, scale=0.12), 352),
                   layer(mamba1(inner=256, state=16, dt_rank=8, conv=4), 64),
                   layer(parallel(heads=2, kv_heads=1, dim=128, window=150, scale=0.09, rheads=2, rdim=128, rvdim=64), 128),
                   layer(attention(heads=4, kv_heads=4, dim=128, vdim=128, window=0, scale=0.09), None)], width=256, vocab=300)
