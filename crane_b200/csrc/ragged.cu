@@ -128,7 +128,8 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, int lds, const
 }
 
 // ---------------------------------------------------------------------------------------------------------------- exact linear
-// 64 x 64 output tile, 16-wide k-steps, 256 threads x (4 x 4) accumulators; each output element sums k = 0 .. K-1 in order.
+// 64 x 64 output tile, 16-wide k-steps, 256 threads x (4 x 4) accumulators; each output element sums its k-steps in order, every
+// k-step summed on its own first (a fixed two-level order, the same for every row count).
 template <int MODE>
 __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict__ A, int lda, const bf16* __restrict__ Wt, int ldw, int M, int N,
                                                          int K, float* __restrict__ C, int ldc, const float* __restrict__ col_scale,
@@ -143,6 +144,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
             sw[k][r] = (n0 + r < N && k0 + k < K) ? __bfloat162float(Wt[(size_t)(n0 + r) * ldw + k0 + k]) : 0.f;
         }
         __syncthreads();
+        float part[4][4] = {};                  // the k-step's own sum first, then one addition into the total: rounding grows with 16 + K / 16 terms, not K
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
             float av[4], wv[4];
@@ -151,8 +153,12 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(av[i], wv[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
         __syncthreads();
     }
 #pragma unroll
