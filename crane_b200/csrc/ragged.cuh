@@ -10,7 +10,11 @@
 //   choice, plain or gated experts, SiLU or clamped units, the score on the expert's input or output; router, counting sort, grouped
 //   linears, ordered combine with a per-column scale, an every-token expert and a sigmoid gate).  See ragged.cu.  Further, in
 //   ragged_mix.cu: a carried causal convolution in front of a sublayer, latent attention (one normalised low-rank row cached per
-//   token), block-diagonal per-head linears, gated linear attention with a decay per key channel, a soft cap on logits.
+//   token), block-diagonal per-head linears, gated linear attention with a decay per key channel, a soft cap on logits.  For layers
+//   whose sublayers read the stream itself and are normalised on their way back: a sinusoidal position vector on the embedding, the
+//   post-norm residual add (one or two normalised inputs), attention scores with a tanh cap, a logarithmic distance penalty or a
+//   distance table, projection biases, a whole-projection norm, unit-RMS values or values taken from the raw keys (ragged.cu), and,
+//   in ragged_scan.cu, the Mamba-1 selective scan and the mLSTM matrix memory.
 #pragma once
 
 #include "common.cuh"
